@@ -1,0 +1,128 @@
+"""ctypes binding of libdeform_sdpa.so (the C ABI declared in include/dsdpa.h).
+
+The library is the product: if it is missing, loading fails loudly.  There is no CPU
+or PyTorch fallback anywhere in this package.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+_HERE = Path(__file__).resolve().parent
+LIB_PATH = _HERE / "libdeform_sdpa.so"
+
+# dsdpa_status
+OK = 0
+ERR_NULL_POINTER = 1
+ERR_BAD_DTYPE = 2
+ERR_BAD_HEAD_DIM = 3
+ERR_BAD_SHAPE = 4
+ERR_MISALIGNED = 5
+ERR_WORKSPACE = 6
+ERR_BAD_FLAGS = 7
+ERR_CUDA = 8
+ERR_DEVICE_TIMEOUT = 9
+ERR_TOO_LARGE = 10
+
+# dsdpa_dtype
+F32, BF16, F16 = 0, 1, 2
+
+# flags
+FLAG_MAPS_FROM_L2 = 0x1
+FLAG_DETERMINISTIC = 0x2
+FLAG_SCATTER_GLOBAL = 0x4
+FLAG_SCATTER = 0x8
+
+# Every symbol include/dsdpa.h declares (checked by the CPU test-suite).
+EXPORTS = (
+    "dsdpa_forward",
+    "dsdpa_backward_workspace_bytes",
+    "dsdpa_backward",
+    "dsdpa_status_string",
+    "dsdpa_version",
+    "dsdpa_last_cuda_error",
+    "dsdpa_device_error",
+    "dsdpa_describe_plan",
+    "dsdpa_probe_l2_read_bandwidth",
+    "dsdpa_probe_shared_read_bandwidth",
+)
+
+
+class Problem(ctypes.Structure):
+    """Mirror of ``struct dsdpa_problem``."""
+    _fields_ = [
+        ("B", ctypes.c_int), ("V", ctypes.c_int), ("Hh", ctypes.c_int),
+        ("W", ctypes.c_int), ("H", ctypes.c_int), ("D", ctypes.c_int), ("S", ctypes.c_int),
+        ("sm_scale", ctypes.c_float), ("dtype", ctypes.c_int), ("flags", ctypes.c_uint),
+    ]
+
+
+class DsdpaError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"libdeform_sdpa: {message} (status {status})")
+        self.status = status
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Load the library once.  Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python {(_HERE / 'build.py')}` "
+            "(there is no fallback path)")
+    L = ctypes.CDLL(str(LIB_PATH))
+    vp, ci = ctypes.c_void_p, ctypes.c_int
+    pp = ctypes.POINTER(Problem)
+    L.dsdpa_forward.argtypes = [pp, vp, vp, vp, vp, vp, vp, ci, vp]
+    L.dsdpa_forward.restype = ci
+    L.dsdpa_backward_workspace_bytes.argtypes = [pp]
+    L.dsdpa_backward_workspace_bytes.restype = ctypes.c_size_t
+    L.dsdpa_backward.argtypes = [pp] + [vp] * 11 + [vp, ctypes.c_size_t, ci, vp]
+    L.dsdpa_backward.restype = ci
+    L.dsdpa_status_string.argtypes = [ci]
+    L.dsdpa_status_string.restype = ctypes.c_char_p
+    L.dsdpa_version.argtypes = []
+    L.dsdpa_version.restype = ci
+    L.dsdpa_last_cuda_error.argtypes = []
+    L.dsdpa_last_cuda_error.restype = ci
+    L.dsdpa_device_error.argtypes = [ci]
+    L.dsdpa_device_error.restype = ci
+    L.dsdpa_describe_plan.argtypes = [pp, ctypes.c_char_p, ctypes.c_size_t]
+    L.dsdpa_describe_plan.restype = ci
+    L.dsdpa_probe_l2_read_bandwidth.argtypes = [vp, ctypes.c_size_t, ci, ci, vp, ctypes.POINTER(ctypes.c_double)]
+    L.dsdpa_probe_l2_read_bandwidth.restype = ci
+    L.dsdpa_probe_shared_read_bandwidth.argtypes = [ci, ci, vp, ctypes.POINTER(ctypes.c_double)]
+    L.dsdpa_probe_shared_read_bandwidth.restype = ci
+    _lib = L
+    return L
+
+
+def status_string(status: int) -> str:
+    return lib().dsdpa_status_string(int(status)).decode()
+
+
+def check(status: int) -> None:
+    """Turn a non-zero dsdpa_status into an exception (ValueError for argument errors,
+    DsdpaError for runtime failures), the way the reference's asserts surface."""
+    if status == OK:
+        return
+    msg = status_string(status)
+    if status == ERR_CUDA:
+        msg += f" (cudaError {lib().dsdpa_last_cuda_error()})"
+        raise DsdpaError(status, msg)
+    if status == ERR_DEVICE_TIMEOUT:
+        raise DsdpaError(status, msg)
+    if status == ERR_BAD_DTYPE:
+        raise NotImplementedError(f"libdeform_sdpa: {msg}")
+    raise ValueError(f"libdeform_sdpa: {msg} (status {status})")
+
+
+def describe_plan(problem: Problem) -> str:
+    buf = ctypes.create_string_buffer(512)
+    check(lib().dsdpa_describe_plan(ctypes.byref(problem), buf, len(buf)))
+    return buf.value.decode()

@@ -1,0 +1,400 @@
+// C ABI of libdeform_sdpa.so: argument checks, planning, launches, status reporting.
+// Declarations and the reference interfaces they replace are in include/dsdpa.h.
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "dsdpa_launch.cuh"
+
+namespace dsdpa {
+
+// Written by a kernel whose bounded wait ran out (one word per device that loads the module).
+__device__ int g_error_word;
+
+static thread_local int t_last_cuda_error = 0;
+
+static int cuda_fail(cudaError_t e) {
+    t_last_cuda_error = (int)e;
+    (void)cudaGetLastError();  // clear the sticky-free error state
+    return DSDPA_ERR_CUDA;
+}
+
+int env_int(const char* name, int fallback) {
+    const char* s = std::getenv(name);
+    if (!s || !*s) return fallback;
+    return std::atoi(s);
+}
+
+int validate_problem(const dsdpa_problem* p) {
+    if (!p) return DSDPA_ERR_NULL_POINTER;
+    if (p->dtype != DSDPA_F32 && p->dtype != DSDPA_BF16 && p->dtype != DSDPA_F16) return DSDPA_ERR_BAD_DTYPE;
+    if (p->D != 16 && p->D != 32 && p->D != 64 && p->D != 128 && p->D != 256) return DSDPA_ERR_BAD_HEAD_DIM;
+    if (p->B <= 0 || p->V <= 0 || p->Hh <= 0 || p->W <= 0 || p->H <= 0 || p->S <= 0) return DSDPA_ERR_BAD_SHAPE;
+    const unsigned known = DSDPA_FLAG_MAPS_FROM_L2 | DSDPA_FLAG_DETERMINISTIC | DSDPA_FLAG_SCATTER_GLOBAL |
+                           DSDPA_FLAG_SCATTER;
+    if (p->flags & ~known) return DSDPA_ERR_BAD_FLAGS;
+    if ((p->flags & DSDPA_FLAG_DETERMINISTIC) && (p->flags & (DSDPA_FLAG_SCATTER | DSDPA_FLAG_SCATTER_GLOBAL)))
+        return DSDPA_ERR_BAD_FLAGS;
+    const long long L = (long long)p->W * p->H;
+    // pixel offsets inside one map and the per-(batch, head) query index are 32-bit
+    if (L * p->D * 4 >= (1ll << 31)) return DSDPA_ERR_BAD_SHAPE;
+    if ((long long)p->V * L >= (1ll << 30)) return DSDPA_ERR_BAD_SHAPE;
+    if ((long long)p->V * p->S >= (1ll << 30)) return DSDPA_ERR_BAD_SHAPE;
+    if ((long long)p->B * p->Hh >= (1ll << 24)) return DSDPA_ERR_BAD_SHAPE;
+    if (!(p->sm_scale == p->sm_scale)) return DSDPA_ERR_BAD_SHAPE;
+    return DSDPA_OK;
+}
+
+TilePlan plan_tiles(const dsdpa_problem& p, bool backward) {
+    const int L = p.W * p.H, VL = p.V * L;
+    const long long map_bytes = (long long)L * p.D * dtype_size(p.dtype);
+    const long long acc_bytes = (long long)L * p.D * 4;
+    const RowGeom rg = row_geom(p.D, p.dtype);
+    const int ch = (p.D * dtype_size(p.dtype) / 16) / rg.G;
+    const char* pre = backward ? "DSDPA_BWD" : "DSDPA_FWD";
+    char name[64];
+    std::snprintf(name, sizeof name, "%s_NW", pre);
+    const int force_nw = env_int(name, 0);
+    std::snprintf(name, sizeof name, "%s_NQ", pre);
+    const int force_nq = env_int(name, 0);
+
+    auto smem_need = [&](int nstage, int nw, bool priv) -> long long {
+        return (long long)nstage * 2 * map_bytes + (priv ? 2 * acc_bytes : 0) + (long long)nw * kPlanRecBytesPerWarp + 16;
+    };
+    TilePlan best{};
+    // mbarrier transaction counts hold 2^20-1 bytes; one stage is two maps
+    const bool can_stage = !(p.flags & DSDPA_FLAG_MAPS_FROM_L2) && smem_need(1, 4, false) <= kPlanSmemMax &&
+                           2 * map_bytes < (1ll << 20);
+    if (can_stage) {
+        const bool want_priv = backward && !(p.flags & DSDPA_FLAG_SCATTER_GLOBAL) && smem_need(1, 8, true) <= kPlanSmemMax;
+        double best_cost = 1e300;
+        const int nqs_fwd[3] = { 4, 2, 1 }, nqs_bwd[2] = { 4, 1 };
+        const int* nqs = backward ? nqs_bwd : nqs_fwd;
+        const int n_nq = backward ? 2 : 3;
+        for (int qi = 0; qi < n_nq; ++qi) {
+            const int nq = nqs[qi];
+            if (force_nq && nq != force_nq) continue;
+            for (int nw = 16; nw >= 4; nw -= 2) {
+                if (force_nw && nw != force_nw) continue;
+                if (smem_need(1, nw, want_priv) > kPlanSmemMax) continue;
+                const int nstage = smem_need(2, nw, want_priv) <= kPlanSmemMax ? 2 : 1;
+                const int cap = nw * rg.NG * nq;
+                const int tiles = (VL + cap - 1) / cap;
+                const int qpt = (VL + tiles - 1) / tiles;
+                const long long ctas = (long long)p.B * p.Hh * tiles;
+                const int rounds = (qpt + nw * rg.NG - 1) / (nw * rg.NG);
+                const long long waves = (ctas + kPlanSMs - 1) / kPlanSMs;
+                // one warp step moves 8*CH 128-bit loads = 32*CH shared-memory wavefronts
+                const double wf = 32.0 * ch * (backward ? 2.5 : 1.0);
+                const double step = nw * wf > 400.0 ? nw * wf : 400.0;
+                const double stage_cost = nstage == 1 ? 2.0 * (double)map_bytes / 48.0 : 0.0;
+                const double flush_cost = want_priv ? 2.0 * (double)acc_bytes / 32.0 : 0.0;
+                const double cta_time = p.V * ((double)rounds * p.S * step + stage_cost + flush_cost + 2000.0);
+                const double cost = (double)waves * cta_time;
+                if (cost < best_cost) {
+                    best_cost = cost;
+                    best.staged = true;
+                    best.priv = want_priv;
+                    best.nstage = nstage;
+                    best.nw = nw;
+                    best.nq = nq;
+                    best.tiles = tiles;
+                    best.q_per_tile = qpt;
+                    best.smem = (size_t)smem_need(nstage, nw, want_priv);
+                    best.ctas = ctas;
+                }
+            }
+        }
+        if (best.staged) return best;
+    }
+    // maps served from L2/L1: one query per group, many small CTAs
+    int nw = force_nw ? force_nw : 8;
+    if (nw * 32 > 256) nw = 8;
+    best.staged = false;
+    best.priv = false;
+    best.nstage = 0;
+    best.nw = nw;
+    best.nq = 1;
+    const int cap = nw * rg.NG;
+    best.tiles = (VL + cap - 1) / cap;
+    best.q_per_tile = cap;
+    best.smem = (size_t)nw * kPlanRecBytesPerWarp + 16;
+    best.ctas = (long long)p.B * p.Hh * best.tiles;
+    return best;
+}
+
+static bool misaligned(const void* p) { return ((uintptr_t)p & 15u) != 0; }
+
+struct DeviceGuard {
+    int prev = -1;
+    cudaError_t err = cudaSuccess;
+    explicit DeviceGuard(int device) {
+        err = cudaGetDevice(&prev);
+        if (err == cudaSuccess && prev != device) err = cudaSetDevice(device);
+    }
+    ~DeviceGuard() {
+        int cur = -1;
+        if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) (void)cudaSetDevice(prev);
+    }
+};
+
+static cudaError_t error_word_ptr(int device, int** out) {
+    static int* cache[64] = {};
+    if (device >= 0 && device < 64 && cache[device]) {
+        *out = cache[device];
+        return cudaSuccess;
+    }
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_error_word);
+    if (e != cudaSuccess) return e;
+    if (device >= 0 && device < 64) cache[device] = (int*)ptr;
+    *out = (int*)ptr;
+    return cudaSuccess;
+}
+
+// ---- bandwidth probes -------------------------------------------------------------
+__device__ unsigned g_probe_sink;  // never read; keeps the probes' loads alive
+
+__global__ void __launch_bounds__(1024, 1) probe_l2_kernel(const uint4* __restrict__ buf, size_t nvec) {
+    // every CTA sweeps the whole buffer, starting at its own offset
+    const size_t start = (size_t)blockIdx.x * 4099u * 1024u % nvec;
+    unsigned acc = 0;
+    const size_t stride = blockDim.x;
+    size_t i = threadIdx.x;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+        size_t a = start + i; if (a >= nvec) a -= nvec;
+        size_t b = start + i + stride; if (b >= nvec) b -= nvec;
+        size_t c = start + i + 2 * stride; if (c >= nvec) c -= nvec;
+        size_t d = start + i + 3 * stride; if (d >= nvec) d -= nvec;
+        const uint4 x0 = ldg128_stream(buf + a), x1 = ldg128_stream(buf + b);
+        const uint4 x2 = ldg128_stream(buf + c), x3 = ldg128_stream(buf + d);
+        acc ^= x0.x ^ x0.w ^ x1.y ^ x1.z ^ x2.x ^ x2.w ^ x3.y ^ x3.z;
+    }
+    if (acc == 0x9e3779b9u) g_probe_sink = acc;
+}
+
+__global__ void __launch_bounds__(1024, 1) probe_smem_kernel(int rounds) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const uint32_t base = smem_addr(smem);
+    // 64 KB window, every lane reads its own 16 bytes of a 512-byte warp line: conflict-free
+    for (uint32_t o = threadIdx.x * 16u; o < 65536u; o += blockDim.x * 16u) sts128(base + o, make_uint4(o, o + 1, o + 2, o + 3));
+    __syncthreads();
+    unsigned acc = 0;
+    uint32_t off = threadIdx.x * 16u;
+    for (int r = 0; r < rounds; ++r) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint4 x = lds128(base + ((off + u * 16384u) & 65535u));
+            acc ^= x.x ^ x.y ^ x.z ^ x.w;
+        }
+        off = (off + 512u * 7u) & 65535u;
+    }
+    if (acc == 0x9e3779b9u) g_probe_sink = acc;
+}
+
+}  // namespace dsdpa
+
+using namespace dsdpa;
+
+extern "C" {
+
+const char* dsdpa_status_string(int status) {
+    switch (status) {
+        case DSDPA_OK: return "ok";
+        case DSDPA_ERR_NULL_POINTER: return "null pointer";
+        case DSDPA_ERR_BAD_DTYPE: return "unsupported dtype (float32, bfloat16 and float16 are supported)";
+        case DSDPA_ERR_BAD_HEAD_DIM: return "head dimension must be one of 16, 32, 64, 128, 256";
+        case DSDPA_ERR_BAD_SHAPE: return "bad shape (non-positive extent or too large)";
+        case DSDPA_ERR_MISALIGNED: return "pointer is not 16-byte aligned";
+        case DSDPA_ERR_WORKSPACE: return "workspace missing or too small";
+        case DSDPA_ERR_BAD_FLAGS: return "unknown or contradictory flags";
+        case DSDPA_ERR_CUDA: return "CUDA runtime error";
+        case DSDPA_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel gave up";
+        case DSDPA_ERR_TOO_LARGE: return "problem exceeds the maximum of this entry point";
+        default: return "unknown status";
+    }
+}
+
+int dsdpa_version(void) { return DSDPA_VERSION; }
+
+int dsdpa_last_cuda_error(void) { return t_last_cuda_error; }
+
+int dsdpa_describe_plan(const dsdpa_problem* p, char* text, size_t cap) {
+    int st = validate_problem(p);
+    if (st != DSDPA_OK) return st;
+    if (!text || cap == 0) return DSDPA_ERR_NULL_POINTER;
+    const TilePlan f = plan_tiles(*p, false), b = plan_tiles(*p, true);
+    std::snprintf(text, cap,
+                  "fwd[%s nstage=%d nw=%d nq=%d tiles=%d q_per_tile=%d ctas=%lld smem=%zu] "
+                  "bwd_scatter[%s%s nstage=%d nw=%d nq=%d tiles=%d q_per_tile=%d ctas=%lld smem=%zu]",
+                  f.staged ? "staged" : "l2", f.nstage, f.nw, f.nq, f.tiles, f.q_per_tile, f.ctas, f.smem,
+                  b.staged ? "staged" : "l2", b.priv ? "+priv" : "", b.nstage, b.nw, b.nq, b.tiles, b.q_per_tile,
+                  b.ctas, b.smem);
+    return DSDPA_OK;
+}
+
+int dsdpa_forward(const dsdpa_problem* p, const void* q, const void* k, const void* v, const float* coords,
+                  void* out, float* lse, int device, void* stream) {
+    int st = validate_problem(p);
+    if (st != DSDPA_OK) return st;
+    if (!q || !k || !v || !coords || !out || !lse) return DSDPA_ERR_NULL_POINTER;
+    if (misaligned(q) || misaligned(k) || misaligned(v) || misaligned(coords) || misaligned(out) || misaligned(lse))
+        return DSDPA_ERR_MISALIGNED;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return cuda_fail(guard.err);
+    int* err_word = nullptr;
+    cudaError_t e = error_word_ptr(device, &err_word);
+    if (e != cudaSuccess) return cuda_fail(e);
+
+    const TilePlan plan = plan_tiles(*p, false);
+    FwdParams fp{};
+    fp.q = q; fp.k = k; fp.v = v; fp.coords = coords; fp.out = out; fp.lse = lse;
+    fp.B = p->B; fp.V = p->V; fp.Hh = p->Hh; fp.W = p->W; fp.H = p->H; fp.L = p->W * p->H; fp.S = p->S;
+    fp.scale2 = p->sm_scale * kLog2e;
+    fp.hw = (float)(p->W - 1) * 0.5f;
+    fp.hh = (float)(p->H - 1) * 0.5f;
+    fp.tiles = plan.tiles;
+    fp.q_per_tile = plan.q_per_tile;
+    fp.nstage = plan.nstage;
+    fp.map_bytes = (unsigned)((size_t)fp.L * p->D * dtype_size(p->dtype));
+    fp.err = err_word;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (p->dtype) {
+        case DSDPA_F32: e = launch_forward<float>(fp, plan, p->D, s); break;
+        case DSDPA_BF16: e = launch_forward<__nv_bfloat16>(fp, plan, p->D, s); break;
+        default: e = launch_forward<__half>(fp, plan, p->D, s); break;
+    }
+    return e == cudaSuccess ? DSDPA_OK : cuda_fail(e);
+}
+
+size_t dsdpa_backward_workspace_bytes(const dsdpa_problem* p) {
+    if (validate_problem(p) != DSDPA_OK) return 0;
+    const size_t n = (size_t)p->B * p->V * p->Hh * p->W * p->H * p->D;
+    // fp32 storage accumulates dK/dV in the outputs themselves
+    return p->dtype == DSDPA_F32 ? 0 : 2 * n * sizeof(float);
+}
+
+int dsdpa_backward(const dsdpa_problem* p, const void* q, const void* k, const void* v, const float* coords,
+                   const void* out, const float* lse, const void* dout, void* dq, void* dk, void* dv,
+                   float* dcoords, void* workspace, size_t workspace_bytes, int device, void* stream) {
+    int st = validate_problem(p);
+    if (st != DSDPA_OK) return st;
+    if (!q || !k || !v || !coords || !out || !lse || !dout || !dq || !dk || !dv) return DSDPA_ERR_NULL_POINTER;
+    if (misaligned(q) || misaligned(k) || misaligned(v) || misaligned(coords) || misaligned(out) || misaligned(lse) ||
+        misaligned(dout) || misaligned(dq) || misaligned(dk) || misaligned(dv) || misaligned(workspace) ||
+        misaligned(dcoords))
+        return DSDPA_ERR_MISALIGNED;
+    if (dcoords) return DSDPA_ERR_BAD_FLAGS;  // coordinate gradient: not in this build
+    const size_t need = dsdpa_backward_workspace_bytes(p);
+    if (need > 0 && (!workspace || workspace_bytes < need)) return DSDPA_ERR_WORKSPACE;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return cuda_fail(guard.err);
+    int* err_word = nullptr;
+    cudaError_t e = error_word_ptr(device, &err_word);
+    if (e != cudaSuccess) return cuda_fail(e);
+    cudaStream_t s = (cudaStream_t)stream;
+
+    const size_t n = (size_t)p->B * p->V * p->Hh * p->W * p->H * p->D;
+    float* dk32 = p->dtype == DSDPA_F32 ? (float*)dk : (float*)workspace;
+    float* dv32 = p->dtype == DSDPA_F32 ? (float*)dv : (float*)workspace + n;
+    if ((e = cudaMemsetAsync(dk32, 0, n * sizeof(float), s)) != cudaSuccess) return cuda_fail(e);
+    if ((e = cudaMemsetAsync(dv32, 0, n * sizeof(float), s)) != cudaSuccess) return cuda_fail(e);
+
+    const TilePlan plan = plan_tiles(*p, true);
+    BwdParams bp{};
+    bp.q = q; bp.k = k; bp.v = v; bp.coords = coords; bp.out = out; bp.lse = lse; bp.dout = dout;
+    bp.dq = dq; bp.dk32 = dk32; bp.dv32 = dv32; bp.dcoords = dcoords;
+    bp.B = p->B; bp.V = p->V; bp.Hh = p->Hh; bp.W = p->W; bp.H = p->H; bp.L = p->W * p->H; bp.S = p->S;
+    bp.sm_scale = p->sm_scale;
+    bp.scale2 = p->sm_scale * kLog2e;
+    bp.hw = (float)(p->W - 1) * 0.5f;
+    bp.hh = (float)(p->H - 1) * 0.5f;
+    bp.tiles = plan.tiles;
+    bp.q_per_tile = plan.q_per_tile;
+    bp.nstage = plan.nstage;
+    bp.map_bytes = (unsigned)((size_t)bp.L * p->D * dtype_size(p->dtype));
+    bp.acc_bytes = (unsigned)((size_t)bp.L * p->D * 4);
+    bp.err = err_word;
+    switch (p->dtype) {
+        case DSDPA_F32: e = launch_backward_scatter<float>(bp, plan, p->D, s); break;
+        case DSDPA_BF16: e = launch_backward_scatter<__nv_bfloat16>(bp, plan, p->D, s); break;
+        default: e = launch_backward_scatter<__half>(bp, plan, p->D, s); break;
+    }
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (p->dtype == DSDPA_BF16) {
+        if ((e = launch_cast_from_f32<__nv_bfloat16>(dk32, dk, n, s)) != cudaSuccess) return cuda_fail(e);
+        if ((e = launch_cast_from_f32<__nv_bfloat16>(dv32, dv, n, s)) != cudaSuccess) return cuda_fail(e);
+    } else if (p->dtype == DSDPA_F16) {
+        if ((e = launch_cast_from_f32<__half>(dk32, dk, n, s)) != cudaSuccess) return cuda_fail(e);
+        if ((e = launch_cast_from_f32<__half>(dv32, dv, n, s)) != cudaSuccess) return cuda_fail(e);
+    }
+    return DSDPA_OK;
+}
+
+int dsdpa_device_error(int device) {
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return cuda_fail(guard.err);
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return cuda_fail(e);
+    int word = 0;
+    if ((e = cudaMemcpyFromSymbol(&word, g_error_word, sizeof(int))) != cudaSuccess) return cuda_fail(e);
+    if (word == 0) return DSDPA_OK;
+    word = 0;
+    if ((e = cudaMemcpyToSymbol(g_error_word, &word, sizeof(int))) != cudaSuccess) return cuda_fail(e);
+    return DSDPA_ERR_DEVICE_TIMEOUT;
+}
+
+static int time_probe(cudaStream_t s, int iters, double bytes_per_iter, double* gbps, void (*launch)(cudaStream_t, void*),
+                      void* ctx) {
+    cudaEvent_t a, b;
+    cudaError_t e;
+    if ((e = cudaEventCreate(&a)) != cudaSuccess) return cuda_fail(e);
+    if ((e = cudaEventCreate(&b)) != cudaSuccess) { cudaEventDestroy(a); return cuda_fail(e); }
+    launch(s, ctx);  // warm-up
+    cudaEventRecord(a, s);
+    for (int i = 0; i < iters; ++i) launch(s, ctx);
+    cudaEventRecord(b, s);
+    e = cudaEventSynchronize(b);
+    float ms = 0.0f;
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, a, b);
+    cudaEventDestroy(a);
+    cudaEventDestroy(b);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e);
+    *gbps = bytes_per_iter * iters / ((double)ms * 1e-3) / 1e9;
+    return DSDPA_OK;
+}
+
+struct L2Ctx { const uint4* buf; size_t nvec; int ctas; };
+static void launch_l2(cudaStream_t s, void* c) {
+    L2Ctx* x = (L2Ctx*)c;
+    probe_l2_kernel<<<x->ctas, 1024, 0, s>>>(x->buf, x->nvec);
+}
+struct SmemCtx { int rounds; int ctas; };
+static void launch_smem(cudaStream_t s, void* c) {
+    SmemCtx* x = (SmemCtx*)c;
+    probe_smem_kernel<<<x->ctas, 1024, 65536, s>>>(x->rounds);
+}
+
+int dsdpa_probe_l2_read_bandwidth(const void* buffer, size_t bytes, int iters, int device, void* stream, double* gbps) {
+    if (!buffer || !gbps) return DSDPA_ERR_NULL_POINTER;
+    if (misaligned(buffer)) return DSDPA_ERR_MISALIGNED;
+    if (bytes < (1u << 20) || iters <= 0) return DSDPA_ERR_BAD_SHAPE;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return cuda_fail(guard.err);
+    L2Ctx c{ (const uint4*)buffer, bytes / 16 / 4096 * 4096, kSMs };
+    return time_probe((cudaStream_t)stream, iters, (double)c.nvec * 16.0 * c.ctas, gbps, launch_l2, &c);
+}
+
+int dsdpa_probe_shared_read_bandwidth(int iters, int device, void* stream, double* gbps) {
+    if (!gbps) return DSDPA_ERR_NULL_POINTER;
+    if (iters <= 0) return DSDPA_ERR_BAD_SHAPE;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return cuda_fail(guard.err);
+    cudaError_t e = cudaFuncSetAttribute(probe_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
+    if (e != cudaSuccess) return cuda_fail(e);
+    SmemCtx c{ 4096, kSMs };
+    return time_probe((cudaStream_t)stream, iters, (double)c.rounds * 8.0 * 16.0 * 1024.0 * c.ctas, gbps, launch_smem, &c);
+}
+
+}  // extern "C"

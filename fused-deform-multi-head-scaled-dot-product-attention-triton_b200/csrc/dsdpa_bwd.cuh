@@ -1,0 +1,296 @@
+// Backward, one-kernel scatter form.
+//
+// Replaces the reference's _bwd_preprocess (ops/triton.py:197-215), _bwd_kernel
+// (ops/triton.py:219-365) and the K pre-scaling / fp32->storage casts around them
+// (ops/triton.py:431-432, 461-462).  Per query-head and sampled key n:
+//     p_n  = exp2(scale2 * q.k~_n - lse)                (recomputed, ops/triton.py:330-333)
+//     ds_n = p_n * (dout.v~_n - delta),  delta = out.dout
+//     dq   = sm_scale * sum_n ds_n k~_n
+//     dK[pix_c] += sm_scale * ds_n * w_c * q,   dV[pix_c] += p_n * w_c * dout   (valid corners c)
+// with per-corner zero padding as in ops/torch.py:14-15.
+//
+// Same work split as the forward kernel (a group of G lanes per query, NQ query slots
+// per group, K/V maps of the current key view staged in shared memory or gathered from
+// L2).  The scatter goes either
+//   PRIV:  into fp32 dK/dV maps of the current key view held in shared memory
+//          (red.shared.add.f32), flushed once per key view with 16-byte vector
+//          reductions (red.global.add.v4.f32), or
+//   else:  straight to global memory with red.global.add.v4.f32.
+// The global accumulators are fp32 ([B,V,Hh,L,D]); for fp32 storage they are the dk/dv
+// outputs themselves.
+#pragma once
+
+#include "dsdpa_fwd.cuh"
+
+namespace dsdpa {
+
+struct BwdParams {
+    const void* q;
+    const void* k;
+    const void* v;
+    const float* coords;
+    const void* out;
+    const float* lse;
+    const void* dout;
+    void* dq;
+    float* dk32;
+    float* dv32;
+    float* dcoords;
+    int B, V, Hh, W, H, L, S;
+    float sm_scale, scale2;
+    float hw, hh;
+    int tiles, q_per_tile, nstage;
+    unsigned map_bytes;   // bytes of one [L, D] map in the storage type
+    unsigned acc_bytes;   // bytes of one [L, D] fp32 map (PRIV)
+    int* err;             // device error word
+};
+
+template <typename T, int D, int NQ, bool STAGED, bool PRIV, int MAXT, int MINB>
+__global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams p) {
+    static_assert(!PRIV || STAGED, "privatised accumulators live next to staged maps");
+    using RC = RowCfg<T, D>;
+    constexpr int G = RC::G, NG = RC::NG, EPL = RC::EPL, CH = RC::CH, EPV = RC::EPV, ROWB = RC::ROWB;
+    extern __shared__ __align__(128) unsigned char smem[];
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int g = lane / G, li = lane % G;
+    const int bh = blockIdx.x / p.tiles, tile = blockIdx.x - bh * p.tiles;
+    const int b = bh / p.Hh, h = bh - b * p.Hh;
+    const int VL = p.V * p.L;
+    const int q0 = tile * p.q_per_tile;
+    const int qend = min(q0 + p.q_per_tile, VL);
+    const int slot_stride = nw * NG;
+
+    const uint32_t smem0 = smem_addr(smem);
+    const uint32_t maps_bytes_all = STAGED ? (uint32_t)p.nstage * 2u * p.map_bytes : 0u;
+    const uint32_t acc_k = smem0 + maps_bytes_all;           // PRIV: fp32 dK map, then dV map
+    const uint32_t acc_v = acc_k + p.acc_bytes;
+    const uint32_t after_acc = maps_bytes_all + (PRIV ? 2u * p.acc_bytes : 0u);
+    const uint32_t rec_w = smem0 + after_acc + (uint32_t)warp * kRecBytesPerWarp;
+    const uint32_t rec_p = rec_w + 32 * 16;
+    const uint32_t bar0 = smem0 + after_acc + (uint32_t)nw * kRecBytesPerWarp;
+
+    const size_t map_stride_view = (size_t)p.Hh * p.map_bytes;
+    const char* kmaps = (const char*)p.k + ((size_t)b * p.V * p.Hh + h) * p.map_bytes;
+    const char* vmaps = (const char*)p.v + ((size_t)b * p.V * p.Hh + h) * p.map_bytes;
+    const size_t acc_stride_view = (size_t)p.Hh * p.L * D;   // floats between views of one head
+    float* dkmaps = p.dk32 + ((size_t)b * p.V * p.Hh + h) * (size_t)p.L * D;
+    float* dvmaps = p.dv32 + ((size_t)b * p.V * p.Hh + h) * (size_t)p.L * D;
+
+    if constexpr (STAGED) {
+        if (threadIdx.x == 0) {
+            mbar_init(bar0, 1);
+            mbar_init(bar0 + 8, 1);
+            fence_mbar_init();
+            fence_proxy_async();
+        }
+        if constexpr (PRIV) {
+            for (uint32_t o = threadIdx.x * 16u; o < 2u * p.acc_bytes; o += blockDim.x * 16u)
+                sts128(acc_k + o, make_uint4(0, 0, 0, 0));
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            mbar_expect_tx(bar0, 2u * p.map_bytes);
+            bulk_g2s_chunked(smem0, kmaps, p.map_bytes, bar0);
+            bulk_g2s_chunked(smem0 + p.map_bytes, vmaps, p.map_bytes, bar0);
+        }
+    }
+
+    // per-slot state that does not depend on the key view
+    float dq[NQ][EPL], lse_q[NQ], delta_q[NQ];
+#pragma unroll
+    for (int j = 0; j < NQ; ++j) {
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) dq[j][e] = 0.0f;
+        lse_q[j] = 0.0f;
+        delta_q[j] = 0.0f;
+        if (q0 + j * slot_stride + warp * NG >= qend) continue;
+        const int qi = min(q0 + j * slot_stride + warp * NG + g, qend - 1);
+        const int vq = qi / p.L, l = qi - vq * p.L;
+        const size_t qrow = (((size_t)b * p.V + vq) * p.Hh + h) * p.L + l;
+        float part = 0.0f;
+#pragma unroll
+        for (int ch = 0; ch < CH; ++ch) {
+            float fo[EPV], fd[EPV];
+            unpack16(ldg128_nc((const char*)p.out + qrow * ROWB + (size_t)(ch * G + li) * 16), fo, (T*)nullptr);
+            unpack16(ldg128_nc((const char*)p.dout + qrow * ROWB + (size_t)(ch * G + li) * 16), fd, (T*)nullptr);
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) part = fmaf(fo[e], fd[e], part);
+        }
+        delta_q[j] = group_sum<G>(part);
+        lse_q[j] = __ldg(p.lse + qrow);
+    }
+
+    for (int vk = 0; vk < p.V; ++vk) {
+        MapReader<T, D, STAGED> kmap, vmap;
+        bool ok = true;
+        if constexpr (STAGED) {
+            const int stage = p.nstage == 2 ? (vk & 1) : 0;
+            if (p.nstage == 2 && vk + 1 < p.V && threadIdx.x == 0) {
+                const uint32_t bar = bar0 + 8u * (uint32_t)((vk + 1) & 1);
+                const uint32_t dst = smem0 + (uint32_t)((vk + 1) & 1) * 2u * p.map_bytes;
+                fence_proxy_async();
+                mbar_expect_tx(bar, 2u * p.map_bytes);
+                bulk_g2s_chunked(dst, kmaps + (size_t)(vk + 1) * map_stride_view, p.map_bytes, bar);
+                bulk_g2s_chunked(dst + p.map_bytes, vmaps + (size_t)(vk + 1) * map_stride_view, p.map_bytes, bar);
+            }
+            const unsigned parity = p.nstage == 2 ? ((unsigned)(vk >> 1) & 1u) : ((unsigned)vk & 1u);
+            ok = mbar_wait_bounded(bar0 + 8u * (uint32_t)stage, parity, p.err);
+            ok = __all_sync(0xffffffffu, ok);
+            kmap.sbase = smem0 + (uint32_t)stage * 2u * p.map_bytes;
+            vmap.sbase = kmap.sbase + p.map_bytes;
+            kmap.gbase = vmap.gbase = nullptr;
+        } else {
+            kmap.gbase = kmaps + (size_t)vk * map_stride_view;
+            vmap.gbase = vmaps + (size_t)vk * map_stride_view;
+            kmap.sbase = vmap.sbase = 0;
+        }
+        float* dkmap = dkmaps + (size_t)vk * acc_stride_view;
+        float* dvmap = dvmaps + (size_t)vk * acc_stride_view;
+
+        if (ok) {
+#pragma unroll
+            for (int j = 0; j < NQ; ++j) {
+                if (q0 + j * slot_stride + warp * NG >= qend) continue;
+                const int qslot = q0 + j * slot_stride + warp * NG + g;
+                const bool live = qslot < qend;       // surplus groups compute but never scatter
+                const int qi = min(qslot, qend - 1);
+                const int vq = qi / p.L, l = qi - vq * p.L;
+                const size_t qrow = (((size_t)b * p.V + vq) * p.Hh + h) * p.L + l;
+                float qf[EPL], dof[EPL];
+#pragma unroll
+                for (int ch = 0; ch < CH; ++ch) {
+                    float f[EPV];
+                    unpack16(ldg128_nc((const char*)p.q + qrow * ROWB + (size_t)(ch * G + li) * 16), f, (T*)nullptr);
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) qf[ch * EPV + e] = f[e] * p.scale2;
+                    unpack16(ldg128_nc((const char*)p.dout + qrow * ROWB + (size_t)(ch * G + li) * 16), f, (T*)nullptr);
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) dof[ch * EPV + e] = f[e];
+                }
+                const float2* cptr = reinterpret_cast<const float2*>(p.coords) +
+                                     ((((size_t)b * p.V + vq) * p.L + l) * p.V + vk) * (size_t)p.S;
+                const float lse = lse_q[j], delta = delta_q[j];
+                for (int s0 = 0; s0 < p.S; s0 += G) {
+                    {
+                        const int s = s0 + li;
+                        float2 c = make_float2(0.0f, 0.0f);
+                        if (s < p.S) c = __ldg(cptr + s);
+                        Corners cr;
+                        float fx, fy;
+                        decode_corners(c.x, c.y, p.W, p.H, p.hw, p.hh, cr, fx, fy);
+                        const uint32_t r = (uint32_t)(li * NG + g) * 16u;
+                        sts128(rec_w + r, make_uint4(__float_as_uint(cr.w[0]), __float_as_uint(cr.w[1]),
+                                                     __float_as_uint(cr.w[2]), __float_as_uint(cr.w[3])));
+                        sts128(rec_p + r, make_uint4((uint32_t)cr.pix[0], (uint32_t)cr.pix[1],
+                                                     (uint32_t)cr.pix[2], (uint32_t)cr.pix[3]));
+                    }
+                    __syncwarp();
+                    const int cnt = min(G, p.S - s0);
+                    for (int i = 0; i < cnt; ++i) {
+                        const uint32_t r = (uint32_t)(i * NG + g) * 16u;
+                        const uint4 wr = lds128(rec_w + r), pr = lds128(rec_p + r);
+                        const float w[4] = { __uint_as_float(wr.x), __uint_as_float(wr.y),
+                                             __uint_as_float(wr.z), __uint_as_float(wr.w) };
+                        const int pix[4] = { (int)pr.x, (int)pr.y, (int)pr.z, (int)pr.w };
+                        float kt[EPL], vt[EPL];
+                        gather_interp<T, D, STAGED>(kmap, pix, w, li, kt);
+                        gather_interp<T, D, STAGED>(vmap, pix, w, li, vt);
+                        float ps = 0.0f, pd = 0.0f;
+#pragma unroll
+                        for (int e = 0; e < EPL; ++e) {
+                            ps = fmaf(qf[e], kt[e], ps);
+                            pd = fmaf(dof[e], vt[e], pd);
+                        }
+                        const float sc = group_sum<G>(ps);
+                        const float dp = group_sum<G>(pd);
+                        const float pe = fast_exp2(sc - lse);
+                        const float ds = pe * (dp - delta);
+#pragma unroll
+                        for (int e = 0; e < EPL; ++e) dq[j][e] = fmaf(ds, kt[e], dq[j][e]);
+                        // qf carries scale2 = sm_scale*log2(e): sm_scale*ds*q = (ds*ln2)*qf
+                        const float ck = ds * kLn2;
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            if (!live || w[c] == 0.0f) continue;
+                            const float wk = ck * w[c], wv = pe * w[c];
+#pragma unroll
+                            for (int ch = 0; ch < CH; ++ch) {
+                                const int e0 = ch * EPV;
+                                const size_t off = (size_t)pix[c] * D + (size_t)(ch * G + li) * EPV;
+                                if constexpr (PRIV) {
+                                    const uint32_t ak = acc_k + (uint32_t)off * 4u, av = acc_v + (uint32_t)off * 4u;
+#pragma unroll
+                                    for (int e = 0; e < EPV; ++e) {
+                                        red_shared_add(ak + 4u * e, wk * qf[e0 + e]);
+                                        red_shared_add(av + 4u * e, wv * dof[e0 + e]);
+                                    }
+                                } else {
+#pragma unroll
+                                    for (int e = 0; e < EPV; e += 4) {
+                                        red_global_add_v4(dkmap + off + e, wk * qf[e0 + e], wk * qf[e0 + e + 1],
+                                                          wk * qf[e0 + e + 2], wk * qf[e0 + e + 3]);
+                                        red_global_add_v4(dvmap + off + e, wv * dof[e0 + e], wv * dof[e0 + e + 1],
+                                                          wv * dof[e0 + e + 2], wv * dof[e0 + e + 3]);
+                                    }
+                                }
+                            }
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+        }
+        if constexpr (STAGED) {
+            if (__syncthreads_or(ok ? 0 : 1)) return;
+            if (p.nstage == 1 && vk + 1 < p.V && threadIdx.x == 0) {
+                fence_proxy_async();
+                mbar_expect_tx(bar0, 2u * p.map_bytes);
+                bulk_g2s_chunked(smem0, kmaps + (size_t)(vk + 1) * map_stride_view, p.map_bytes, bar0);
+                bulk_g2s_chunked(smem0 + p.map_bytes, vmaps + (size_t)(vk + 1) * map_stride_view, p.map_bytes, bar0);
+            }
+            if constexpr (PRIV) {
+                // flush this key view's private dK/dV maps with vector reductions and clear them
+                const uint32_t nvec = p.acc_bytes / 16u;
+                for (uint32_t i = threadIdx.x; i < 2u * nvec; i += blockDim.x) {
+                    const uint32_t sa = acc_k + i * 16u;
+                    const uint4 r = lds128(sa);
+                    if ((r.x | r.y | r.z | r.w) == 0u) continue;
+                    float* dst = (i < nvec ? dkmap + (size_t)i * 4 : dvmap + (size_t)(i - nvec) * 4);
+                    red_global_add_v4(dst, __uint_as_float(r.x), __uint_as_float(r.y), __uint_as_float(r.z),
+                                      __uint_as_float(r.w));
+                    sts128(sa, make_uint4(0, 0, 0, 0));
+                }
+                __syncthreads();
+            }
+        }
+    }
+
+#pragma unroll
+    for (int j = 0; j < NQ; ++j) {
+        const int qi = q0 + j * slot_stride + warp * NG + g;
+        if (qi >= qend) continue;
+        const int vq = qi / p.L, l = qi - vq * p.L;
+        const size_t qrow = (((size_t)b * p.V + vq) * p.Hh + h) * p.L + l;
+#pragma unroll
+        for (int ch = 0; ch < CH; ++ch) {
+            float f[EPV];
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) f[e] = dq[j][ch * EPV + e] * p.sm_scale;
+            stg128((char*)p.dq + qrow * ROWB + (size_t)(ch * G + li) * 16, pack16(f, (T*)nullptr));
+        }
+    }
+}
+
+// fp32 accumulators -> storage type, 8 elements per thread.
+template <typename T>
+__global__ void cast_from_f32_kernel(const float* __restrict__ src, T* __restrict__ dst, size_t n8) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+        const uint4 a = ldg128_stream(src + i * 8), c = ldg128_stream(src + i * 8 + 4);
+        const float f[8] = { __uint_as_float(a.x), __uint_as_float(a.y), __uint_as_float(a.z), __uint_as_float(a.w),
+                             __uint_as_float(c.x), __uint_as_float(c.y), __uint_as_float(c.z), __uint_as_float(c.w) };
+        stg128(dst + i * 8, pack16(f, (T*)nullptr));
+    }
+}
+
+}  // namespace dsdpa

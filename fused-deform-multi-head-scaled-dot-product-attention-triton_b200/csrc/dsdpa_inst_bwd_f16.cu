@@ -1,0 +1,2 @@
+#define DSDPA_T __half
+#include "dsdpa_inst_bwd.inc"

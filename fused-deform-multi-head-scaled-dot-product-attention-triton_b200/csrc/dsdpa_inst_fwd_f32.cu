@@ -1,0 +1,2 @@
+#define DSDPA_T float
+#include "dsdpa_inst_fwd.inc"

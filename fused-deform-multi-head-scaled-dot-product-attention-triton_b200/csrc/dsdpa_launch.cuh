@@ -1,0 +1,89 @@
+// Launch dispatch: (dtype, head dim, slots, variant) -> kernel instantiation.
+// The instantiations live in one translation unit per storage type and direction
+// (dsdpa_inst_*.cu) so that they compile in parallel; this header is what they share
+// with the C-ABI translation unit.
+#pragma once
+
+#include "dsdpa_bwd.cuh"
+#include "dsdpa_plan.h"
+
+namespace dsdpa {
+
+template <typename T>
+cudaError_t launch_forward(const FwdParams& p, const TilePlan& plan, int D, cudaStream_t stream);
+template <typename T>
+cudaError_t launch_backward_scatter(const BwdParams& p, const TilePlan& plan, int D, cudaStream_t stream);
+template <typename T>
+cudaError_t launch_cast_from_f32(const float* src, void* dst, size_t n, cudaStream_t stream);
+
+// Thread limits the variants are compiled for (the plan must stay within them).
+constexpr int kStagedMaxThreads = 512;
+constexpr int kL2MaxThreads = 256;
+
+namespace detail {
+
+// Opt the kernel in to the full 227 KB of dynamic shared memory, once per device.
+// `done` must be a flag array owned by the calling instantiation: the kernels of one
+// family all share a function-pointer type, so a static in here would be shared too.
+template <typename K>
+inline cudaError_t allow_big_smem(K kern, bool (&done)[64]) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64 && done[dev]) return cudaSuccess;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+    if (e == cudaSuccess && dev >= 0 && dev < 64) done[dev] = true;
+    return e;
+}
+
+template <typename T, int D, int NQ, bool STAGED>
+inline cudaError_t fwd_one(const FwdParams& p, const TilePlan& plan, cudaStream_t stream) {
+    auto kern = fwd_kernel<T, D, NQ, STAGED, STAGED ? kStagedMaxThreads : kL2MaxThreads, STAGED ? 1 : 2>;
+    static bool done[64] = {};  // a benign race at worst repeats the attribute call
+    cudaError_t e = allow_big_smem(kern, done);
+    if (e != cudaSuccess) return e;
+    kern<<<(unsigned)plan.ctas, plan.nw * 32, plan.smem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <typename T, int D>
+inline cudaError_t fwd_d(const FwdParams& p, const TilePlan& plan, cudaStream_t stream) {
+    if (!plan.staged) return fwd_one<T, D, 1, false>(p, plan, stream);
+    switch (plan.nq) {
+        case 1: return fwd_one<T, D, 1, true>(p, plan, stream);
+        case 2: return fwd_one<T, D, 2, true>(p, plan, stream);
+        case 4: return fwd_one<T, D, 4, true>(p, plan, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+template <typename T, int D, int NQ, bool STAGED, bool PRIV>
+inline cudaError_t bwd_one(const BwdParams& p, const TilePlan& plan, cudaStream_t stream) {
+    auto kern = bwd_scatter_kernel<T, D, NQ, STAGED, PRIV, STAGED ? kStagedMaxThreads : kL2MaxThreads, STAGED ? 1 : 2>;
+    static bool done[64] = {};  // a benign race at worst repeats the attribute call
+    cudaError_t e = allow_big_smem(kern, done);
+    if (e != cudaSuccess) return e;
+    kern<<<(unsigned)plan.ctas, plan.nw * 32, plan.smem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <typename T, int D>
+inline cudaError_t bwd_d(const BwdParams& p, const TilePlan& plan, cudaStream_t stream) {
+    if (!plan.staged) return bwd_one<T, D, 1, false, false>(p, plan, stream);
+    if (plan.priv) {
+        switch (plan.nq) {
+            case 1: return bwd_one<T, D, 1, true, true>(p, plan, stream);
+            case 4: return bwd_one<T, D, 4, true, true>(p, plan, stream);
+            default: return cudaErrorInvalidValue;
+        }
+    }
+    switch (plan.nq) {
+        case 1: return bwd_one<T, D, 1, true, false>(p, plan, stream);
+        case 4: return bwd_one<T, D, 4, true, false>(p, plan, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace detail
+
+}  // namespace dsdpa

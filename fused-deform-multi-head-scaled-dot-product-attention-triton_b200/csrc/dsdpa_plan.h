@@ -1,0 +1,51 @@
+// Host-side planning: which kernel variant and tile shape a problem runs with.
+// Stands where the reference's 81-configuration autotune sits (ops/triton.py:10-25):
+// the choice is made from the shape, once, on the host, by a small cost model.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+#include "../../include/dsdpa.h"
+
+namespace dsdpa {
+
+constexpr int kPlanSMs = 148;
+constexpr int kPlanSmemMax = 232448;
+constexpr int kPlanRecBytesPerWarp = 1024;
+
+inline int dtype_size(int dtype) { return dtype == DSDPA_F32 ? 4 : 2; }
+
+struct RowGeom {
+    int G;   // lanes per row
+    int NG;  // groups per warp
+};
+inline RowGeom row_geom(int D, int dtype) {
+    int vec = D * dtype_size(dtype) / 16;
+    RowGeom r;
+    r.G = vec < 32 ? vec : 32;
+    r.NG = 32 / r.G;
+    return r;
+}
+
+struct TilePlan {
+    bool staged;       // K/V maps of one key view staged in shared memory
+    bool priv;         // backward only: dK/dV maps privatised in shared memory
+    int nstage;        // map buffers (staged)
+    int nw;            // warps per CTA
+    int nq;            // query slots per group (template parameter)
+    int tiles;         // tiles per (batch, head)
+    int q_per_tile;
+    size_t smem;       // dynamic shared memory per CTA
+    long long ctas;
+};
+
+// Environment overrides for experiments: DSDPA_<which>_NW, DSDPA_<which>_NQ.
+int env_int(const char* name, int fallback);
+
+// `backward`: plan for the scatter kernel (it can additionally privatise dK/dV).
+TilePlan plan_tiles(const dsdpa_problem& p, bool backward);
+
+int validate_problem(const dsdpa_problem* p);
+
+}  // namespace dsdpa

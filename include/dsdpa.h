@@ -1,0 +1,143 @@
+/*
+ * dsdpa.h -- C ABI of the B200 (sm_100a) fused deformable multi-head
+ * scaled-dot-product attention library (libdeform_sdpa.so).
+ *
+ * The library replaces the device side of the reference's fused operator:
+ * the Triton kernels _fwd_kernel (ops/triton.py:27-194), _bwd_preprocess
+ * (ops/triton.py:197-215) and _bwd_kernel (ops/triton.py:219-365), and the tensor
+ * passes the operator's host code runs around them (coordinate scaling,
+ * zero fills, K pre-scaling and dtype casts, ops/triton.py:381-383, 389,
+ * 427-432, 461-462).  Results follow the reference's pure-PyTorch path
+ * (ops/torch.py:5-28): bilinear sampling with align_corners=True and zero padding
+ * per corner.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer of the device passed in `device`, 16-byte
+ *     aligned, to a contiguous tensor.  The library borrows them for the duration of
+ *     the enqueued work and never allocates or frees memory.
+ *   - Every call is asynchronous on `stream` (a cudaStream_t passed as void*; NULL
+ *     is the legacy default stream) and returns a dsdpa_status.  No call throws,
+ *     aborts or synchronises the device, except dsdpa_device_error().
+ *   - Tensor layouts are the reference's (README.md:35-38):
+ *       q, k, v, out, dout, dq, dk, dv : [B, V, Hh, L, D]   L = W*H, pixel (x,y) = y*W+x
+ *       coords                         : [B, V, L, V, S, 2] fp32, (x, y) normalised to [0,1]
+ *       lse                            : [B, V, Hh, L]      fp32, base-2 log-sum-exp
+ */
+#ifndef DSDPA_H_
+#define DSDPA_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DSDPA_VERSION 100
+
+typedef enum dsdpa_status {
+    DSDPA_OK = 0,
+    DSDPA_ERR_NULL_POINTER = 1,
+    DSDPA_ERR_BAD_DTYPE = 2,       /* the reference raises NotImplementedError (ops/triton.py:375) */
+    DSDPA_ERR_BAD_HEAD_DIM = 3,    /* the reference asserts D in {16,32,64,128,256} (ops/triton.py:386) */
+    DSDPA_ERR_BAD_SHAPE = 4,       /* a non-positive extent, or more elements than the index type holds */
+    DSDPA_ERR_MISALIGNED = 5,      /* a pointer that is not 16-byte aligned */
+    DSDPA_ERR_WORKSPACE = 6,       /* workspace missing or smaller than dsdpa_backward_workspace_bytes */
+    DSDPA_ERR_BAD_FLAGS = 7,
+    DSDPA_ERR_CUDA = 8,            /* a CUDA runtime call failed; see dsdpa_last_cuda_error() */
+    DSDPA_ERR_DEVICE_TIMEOUT = 9,  /* a bounded wait inside a kernel gave up (dsdpa_device_error) */
+    DSDPA_ERR_TOO_LARGE = 10       /* beyond a stated maximum of the entry point */
+} dsdpa_status;
+
+typedef enum dsdpa_dtype {
+    DSDPA_F32 = 0,
+    DSDPA_BF16 = 1,
+    DSDPA_F16 = 2
+} dsdpa_dtype;
+
+/* Flags (OR-ed).  0 selects the default path for the shape. */
+#define DSDPA_FLAG_MAPS_FROM_L2    0x1u /* never stage K/V maps in shared memory: gather with read-only loads */
+#define DSDPA_FLAG_DETERMINISTIC   0x2u /* backward: two-pass dK/dV with a fixed summation order */
+#define DSDPA_FLAG_SCATTER_GLOBAL  0x4u /* backward scatter: reductions straight to global memory,
+                                           no shared-memory privatised accumulation */
+#define DSDPA_FLAG_SCATTER         0x8u /* backward: force the one-kernel scatter form */
+
+/* Problem description shared by all entry points. */
+typedef struct dsdpa_problem {
+    int B;          /* batch */
+    int V;          /* views (query views == key views) */
+    int Hh;         /* attention heads */
+    int W, H;       /* feature-map width and height; L = W*H pixels */
+    int D;          /* head dimension, one of 16, 32, 64, 128, 256 */
+    int S;          /* sampling points per (query, key view) */
+    float sm_scale; /* softmax scale applied to q.k */
+    int dtype;      /* dsdpa_dtype of q, k, v, out, dout, dq, dk, dv */
+    unsigned flags; /* DSDPA_FLAG_* */
+} dsdpa_problem;
+
+/*
+ * Forward.  Replaces _fused_deform_sdpa.forward's device work (ops/triton.py:379-416):
+ * writes out (storage dtype) and lse (what the reference calls M, ops/triton.py:187-190).
+ */
+int dsdpa_forward(const dsdpa_problem* p,
+                  const void* q, const void* k, const void* v, const float* coords,
+                  void* out, float* lse, int device, void* stream);
+
+/*
+ * Bytes of scratch dsdpa_backward needs for this problem (0 is possible).
+ * Depends on the shape, dtype and flags only.
+ */
+size_t dsdpa_backward_workspace_bytes(const dsdpa_problem* p);
+
+/*
+ * Backward.  Replaces _fused_deform_sdpa.backward's device work (ops/triton.py:419-464):
+ * delta = sum(out*dout) (ops/triton.py:197-215), dq (ops/triton.py:339, 362-365) and the
+ * dK/dV scatter (ops/triton.py:342-360), including the zero fill of the accumulators and
+ * the cast to the storage dtype.  dq, dk, dv are overwritten.
+ * dcoords may be NULL (the reference returns no coordinate gradient, ops/triton.py:464);
+ * when given it receives d(loss)/d(coords), fp32, same shape as coords.
+ */
+int dsdpa_backward(const dsdpa_problem* p,
+                   const void* q, const void* k, const void* v, const float* coords,
+                   const void* out, const float* lse, const void* dout,
+                   void* dq, void* dk, void* dv, float* dcoords,
+                   void* workspace, size_t workspace_bytes, int device, void* stream);
+
+/* Human-readable name of a dsdpa_status. */
+const char* dsdpa_status_string(int status);
+
+/* DSDPA_VERSION of the loaded library. */
+int dsdpa_version(void);
+
+/* cudaError_t value of the last failed CUDA call of this thread's last DSDPA_ERR_CUDA. */
+int dsdpa_last_cuda_error(void);
+
+/*
+ * Synchronises `device` and returns DSDPA_ERR_DEVICE_TIMEOUT if any kernel of this
+ * library recorded that a bounded wait ran out since the last call (clearing the
+ * record), DSDPA_OK otherwise.
+ */
+int dsdpa_device_error(int device);
+
+/*
+ * How the library would run this problem: fills `text` (up to `cap` bytes, NUL
+ * terminated) with a one-line description (paths, tile sizes, shared memory).
+ */
+int dsdpa_describe_plan(const dsdpa_problem* p, char* text, size_t cap);
+
+/*
+ * Measurement helpers used by the benchmark to obtain roofline denominators on the
+ * device at hand.  Each runs a read-only kernel on `stream` `iters` times after one
+ * warm-up, times it with CUDA events on that stream, synchronises, and returns GB/s
+ * in *gbps.
+ *   l2:      every SM reads a `bytes`-sized buffer (<= L2 size, caller-provided) with
+ *            128-bit read-only loads.
+ *   shared:  every SM reads its own shared memory with conflict-free 128-bit loads.
+ */
+int dsdpa_probe_l2_read_bandwidth(const void* buffer, size_t bytes, int iters,
+                                  int device, void* stream, double* gbps);
+int dsdpa_probe_shared_read_bandwidth(int iters, int device, void* stream, double* gbps);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DSDPA_H_ */
