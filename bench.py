@@ -1,0 +1,426 @@
+#!/usr/bin/env python
+"""Benchmark of the fused deformable SDPA hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--config C5] [--mode fwdbwd|fwd]
+
+One "step" is one pass of the hot path over the workload: forward and backward
+(dq, dk, dv) of the operator through the C ABI.  The workload at every N is the
+scaling configuration C5 (B=32, V=8, S=32, heads=16, D=64, 28x28 map, bf16, uniform
+coordinates), the total split by batch over the N ranks ("strong" scaling) with the
+outputs gathered to rank 0 inside the timed region.  Rank 0 prints ONE JSON line.
+
+`--impl reference` times the CPU implementation of the same path (the C oracle port of
+the reference's ops/torch.py, all host threads) on a bounded sample of the workload.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from dataclasses import replace
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "query-heads/sec (forward+backward)"
+METRIC_FWD = "query-heads/sec (forward)"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="C5")
+    ap.add_argument("--mode", default="fwdbwd", choices=["fwdbwd", "fwd"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+# --------------------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------
+# CPU arm (the reference's path restated in C, test infrastructure)
+# --------------------------------------------------------------------------------------
+def cpu_sample(cfg, mode, steps, warmup, target_s=15.0):
+    """Times the oracle on a bounded sample of the workload: whole batch elements (all
+    their heads), as many as keep one step near `target_s` seconds on this host."""
+    from oracle import oracle as orc
+    import ops
+    inp = ops.backend.inputs
+    threads = orc.max_threads()
+    per_batch_qh = cfg.V * cfg.Hh * cfg.L
+
+    def run(q, k, v, coords, dout):
+        t0 = time.perf_counter()
+        orc.forward(q, k, v, coords, cfg.W, cfg.H, cfg.sm_scale)
+        if mode == "fwdbwd":
+            orc.backward(q, k, v, coords, dout, cfg.W, cfg.H, cfg.sm_scale)
+        return time.perf_counter() - t0
+
+    # calibration: enough batch elements to give every thread a (batch, head) slice
+    nb_cal = max(1, min(cfg.B, (threads + cfg.Hh - 1) // cfg.Hh))
+    cal = inp.make_inputs(replace(cfg, B=nb_cal))
+    t_cal = run(*cal)
+    nb = max(nb_cal, min(cfg.B, int(nb_cal * target_s / max(t_cal, 1e-3))))
+    data = cal if nb == nb_cal else inp.make_inputs(replace(cfg, B=nb))
+    for _ in range(warmup):
+        run(*data)
+    times = [run(*data) for _ in range(steps)]
+    t = sum(times) / len(times)
+    qh = nb * per_batch_qh
+    return {
+        "value": qh / t, "ms_per_step": t * 1e3, "cores": threads, "kind": "port",
+        "unit": "query-heads/sec",
+        "sample": f"{nb} of {cfg.B} batch elements of {cfg.name} ({nb * cfg.Hh} (batch, head) slices, "
+                  f"{qh} query-heads per step), {'forward+backward' if mode == 'fwdbwd' else 'forward'}",
+    }
+
+
+def run_reference_arm(args):
+    import ops
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = ops.backend.inputs.CONFIGS[args.config]
+    steps = max(1, min(args.steps, 3))
+    warm = 1 if args.warmup > 0 else 0
+    r = cpu_sample(cfg, args.mode, steps, warm)
+    line = {
+        "impl": "reference",
+        "metric": METRIC if args.mode == "fwdbwd" else METRIC_FWD,
+        "value": r["value"], "unit": "query-heads/sec", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
+        "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16" if cfg.elem_size() == 2 else "f32", "data": "synthetic (seeded)",
+        "config": config_dict(cfg, args, 1),
+        "cpu_baseline": {"value": r["value"], "unit": r["unit"], "cores": r["cores"], "kind": r["kind"],
+                         "sample": r["sample"]},
+        "e2e": {"value": r["value"], "unit": "query-heads/sec", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def config_dict(cfg, args, world):
+    return {
+        "workload": f"{cfg.name}: B={cfg.B} V={cfg.V} S={cfg.S} heads={cfg.Hh} D={cfg.D} map={cfg.W}x{cfg.H} "
+                    f"sm_scale={cfg.sm_scale:g} {str(cfg.dtype).replace('torch.', '')} coords={cfg.coords}",
+        "step": "forward+backward (dq, dk, dv)" if args.mode == "fwdbwd" else "forward",
+        "sharding": f"batch over {world} rank(s), outputs gathered to rank 0" if world > 1 else "single GPU",
+        "l2": "inputs (1.6 GB per step) are larger than L2; no explicit flush",
+    }
+
+
+# --------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import ops
+    be = ops.backend
+    cabi, inp, part = be.cabi, be.inputs, be.partition
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path "
+                         "(use --impl reference for the CPU arm)")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    cfg = inp.CONFIGS[args.config]
+    plan = part.shard_plan(cfg.B, cfg.Hh, world)
+    shard = plan[rank]
+    nb = shard.b1 - shard.b0
+    nh = shard.h1 - shard.h0
+    lib = cabi.lib()
+    fwd_only = args.mode == "fwd"
+
+    # ---- synthetic inputs of this rank's shard, drawn on the device (seeded per batch element)
+    def draw(b):
+        g = torch.Generator(device=dev).manual_seed(inp.SEED0 + 4000 + b)
+        shape = (cfg.V, cfg.Hh, cfg.L, cfg.D)
+        q = torch.randn(shape, generator=g, device=dev).to(cfg.dtype)
+        k = torch.randn(shape, generator=g, device=dev).to(cfg.dtype)
+        v = torch.randn(shape, generator=g, device=dev).to(cfg.dtype)
+        do = torch.randn(shape, generator=g, device=dev).to(cfg.dtype)
+        cs = (cfg.V, cfg.L, cfg.V, cfg.S, 2)
+        if cfg.coords == "uniform":
+            c = torch.rand(cs, generator=g, device=dev)
+        elif cfg.coords == "oob":
+            c = torch.rand(cs, generator=g, device=dev) * 1.2 - 0.1
+        else:
+            ls = torch.arange(cfg.L, device=dev)
+            ctr = torch.stack([(ls % cfg.W).float() / max(cfg.W - 1, 1), (ls // cfg.W).float() / max(cfg.H - 1, 1)], -1)
+            near = (ctr.view(1, cfg.L, 1, 1, 2) + cfg.sigma * torch.randn(cs, generator=g, device=dev)).clamp_(0, 1)
+            if cfg.coords == "clustered":
+                c = near
+            else:
+                uni = torch.rand(cs, generator=g, device=dev)
+                pick = torch.rand(cs[:-1], generator=g, device=dev) < 0.5
+                c = torch.where(pick.unsqueeze(-1), uni, near)
+        sl = slice(shard.h0, shard.h1)
+        return q[:, sl], k[:, sl], v[:, sl], do[:, sl], c
+
+    parts = [draw(b) for b in range(shard.b0, shard.b1)]
+    q, k, v, dout = (torch.stack([p[i] for p in parts]).contiguous() for i in range(4))
+    coords = torch.stack([p[4] for p in parts]).contiguous()
+    del parts
+    full_shape = (cfg.B, cfg.V, cfg.Hh, cfg.L, cfg.D)
+
+    def gather(t):
+        if world == 1:
+            return t
+        return part.gather_to_root(t, plan, full_shape, root=0)
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+    fwd_ms, bwd_ms = [], []
+
+    def step(record):
+        e0, e1, e2 = ev(), ev(), ev()
+        e0.record()
+        out, lse = be.forward_raw(q, k, v, coords, cfg.W, cfg.H, cfg.sm_scale)
+        e1.record()
+        res = [out]
+        if not fwd_only:
+            dq, dk, dv, _ = be.backward_raw(q, k, v, coords, out, lse, dout, cfg.W, cfg.H, cfg.sm_scale)
+            e2.record()
+            res += [dq, dk, dv]
+        gathered = [gather(t) for t in res]
+        if record:
+            fwd_ms.append((e0, e1))
+            if not fwd_only:
+                bwd_ms.append((e1, e2))
+        return gathered
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn(False)
+        barrier()
+        a, b = ev(), ev()
+        a.record()
+        for _ in range(steps):
+            fn(True)
+        b.record()
+        barrier()
+        ms = torch.tensor([a.elapsed_time(b)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    launches0 = lib.dsdpa_kernel_launches()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    total_ms = timed(step, args.steps, max(args.warmup, 3))
+    clocks = sampler.stop() if sampler else None
+    launches_all = lib.dsdpa_kernel_launches() - launches0
+    cabi.check(lib.dsdpa_device_error(local_rank))
+    # launches inside the timed region only (warm-up steps launch the same kernels)
+    steps_run = args.steps + max(args.warmup, 3)
+    launches = launches_all * args.steps // steps_run
+
+    ms_step = total_ms / args.steps
+    value = cfg.query_heads / (ms_step * 1e-3)
+    f_ms = statistics.mean(a.elapsed_time(b) for a, b in fwd_ms)
+    b_ms = statistics.mean(a.elapsed_time(b) for a, b in bwd_ms) if bwd_ms else None
+
+    # ---- forward only (extra, same timing rules)
+    fwd_value = None
+    if not fwd_only:
+        def fstep(_record):
+            out, _lse = be.forward_raw(q, k, v, coords, cfg.W, cfg.H, cfg.sm_scale)
+            return gather(out)
+        fwd_total = timed(fstep, args.steps, 3)
+        fwd_value = cfg.query_heads / (fwd_total / args.steps * 1e-3)
+
+    # ---- end to end: pinned host inputs in, results back out, through the operator's API
+    e2e = None
+    if not args.no_e2e:
+        hq, hk, hv, hdo, hc = (t.cpu().pin_memory() for t in (q, k, v, dout, coords))
+        h_out = [torch.empty_like(hq).pin_memory() for _ in range(1 if fwd_only else 4)]
+        h2d = sum(t.numel() * t.element_size() for t in ((hq, hk, hv, hc) if fwd_only else (hq, hk, hv, hc, hdo)))
+        d2h = sum(t.numel() * t.element_size() for t in h_out)
+
+        def estep(_record):
+            dq_, dk_, dv_ = (t.to(dev, non_blocking=True) for t in (hq, hk, hv))
+            dc_ = hc.to(dev, non_blocking=True)
+            if fwd_only:
+                out_ = be.deform_sdpa_triton(dq_, dk_, dv_, dc_, cfg.W, cfg.H, cfg.sm_scale)
+                res = [out_]
+            else:
+                dq_.requires_grad_(True); dk_.requires_grad_(True); dv_.requires_grad_(True)
+                out_ = be.deform_sdpa_triton(dq_, dk_, dv_, dc_, cfg.W, cfg.H, cfg.sm_scale)
+                out_.backward(hdo.to(dev, non_blocking=True))
+                res = [out_.detach(), dq_.grad, dk_.grad, dv_.grad]
+            for dst, src in zip(h_out, res):
+                dst.copy_(src, non_blocking=True)
+        e_total = timed(estep, max(2, min(args.steps, 5)), 3)
+        e_ms = e_total / max(2, min(args.steps, 5))
+        # bytes are per rank; the job moves world times as much
+        e2e = {"value": cfg.query_heads / (e_ms * 1e-3), "unit": "query-heads/sec", "ms_per_step": e_ms,
+               "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world}
+        del hq, hk, hv, hdo, hc, h_out
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the forward kernel and of the backward
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    hbm_peak, hbm_src = 6650.0, "fallback"
+    if peaks_file.exists():
+        try:
+            hbm_peak = float(json.loads(peaks_file.read_text())["hbm_gbs"])
+            hbm_src = "measured"
+        except (KeyError, ValueError):
+            pass
+    g = ctypes.c_double()
+    buf = torch.empty(32 << 20, dtype=torch.uint8, device=dev)
+    cabi.check(lib.dsdpa_probe_l2_read_bandwidth(ctypes.c_void_p(buf.data_ptr()), buf.numel(), 5, local_rank, None,
+                                                 ctypes.byref(g)))
+    l2_peak = g.value
+    cabi.check(lib.dsdpa_probe_shared_read_bandwidth(5, local_rank, None, ctypes.byref(g)))
+    smem_peak = g.value
+    qh_rank = nb * cfg.V * nh * cfg.L
+    gather_b = qh_rank * cfg.gather_bytes_per_qh()
+    hbm_f = qh_rank * cfg.hbm_bytes_per_qh(False)
+    hbm_b = qh_rank * cfg.hbm_bytes_per_qh(True)
+    dt = {torch.float32: cabi.F32, torch.bfloat16: cabi.BF16, torch.float16: cabi.F16}[cfg.dtype]
+    prob = cabi.Problem(nb, cfg.V, nh, cfg.W, cfg.H, cfg.D, cfg.S, cfg.sm_scale, dt, 0)
+    plan_text = cabi.describe_plan(prob)
+    staged = plan_text.startswith("fwd[staged")
+    gather_gbs = gather_b / (f_ms * 1e-3) / 1e9
+    roofline = {
+        "kernel": "fwd_kernel (forward, one launch per step)",
+        "bound": "l2", "achieved": gather_gbs, "peak": l2_peak, "unit": "GB/s", "frac": gather_gbs / l2_peak,
+        "traffic": None,
+        "algorithmic_bytes": "K/V gather bytes: query-heads x V*S keys x 8 rows x D x elem_size",
+        "peak_source": "L2 read bandwidth measured in this run (32 MB resident buffer, 128-bit loads)",
+        "note": ("K/V maps are staged in shared memory, so the gather is served above the L2 roofline; "
+                 "see shared_memory" if staged else "K/V rows gathered from L2/L1"),
+        "shared_memory": {"achieved": gather_gbs, "peak": smem_peak, "unit": "GB/s", "frac": gather_gbs / smem_peak,
+                          "peak_source": "shared-memory read bandwidth measured in this run"},
+        "hbm": {"bound": "hbm", "achieved": hbm_f / (f_ms * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
+                "frac": hbm_f / (f_ms * 1e-3) / 1e9 / hbm_peak, "peak_source": f"MEASURED_PEAKS.json ({hbm_src})",
+                "algorithmic_bytes": "compulsory HBM bytes: q,k,v,out once + coords once + lse"},
+        "ms_per_launch": f_ms,
+    }
+    if b_ms is not None:
+        roofline["backward"] = {
+            "ms": b_ms, "gather_GBps": gather_b / (b_ms * 1e-3) / 1e9,
+            "scatter_GBps": qh_rank * cfg.N * 8 * cfg.D * 4 / (b_ms * 1e-3) / 1e9,
+            "hbm_GBps": hbm_b / (b_ms * 1e-3) / 1e9, "hbm_frac": hbm_b / (b_ms * 1e-3) / 1e9 / hbm_peak,
+        }
+
+    cpu = None
+    if not args.no_cpu_baseline and world == 1:
+        cpu = cpu_sample(cfg, args.mode, 1, 0)
+        cpu = {"value": cpu["value"], "unit": cpu["unit"], "cores": cpu["cores"], "kind": cpu["kind"],
+               "sample": cpu["sample"]}
+
+    line = {
+        "metric": METRIC if not fwd_only else METRIC_FWD,
+        "value": value, "unit": "query-heads/sec", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16" if cfg.dtype == torch.bfloat16 else str(cfg.dtype).replace("torch.", ""),
+        "data": "synthetic (seeded, drawn on the device)",
+        "config": config_dict(cfg, args, world),
+        "fwd": {"value": fwd_value, "unit": "query-heads/sec", "kernel_ms": f_ms} if fwd_value else None,
+        "bwd_ms": b_ms,
+        "roofline": roofline,
+        "cpu_baseline": cpu,
+        "e2e": e2e,
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "plan": plan_text,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

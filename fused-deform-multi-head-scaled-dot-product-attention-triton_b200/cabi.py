@@ -41,6 +41,7 @@ EXPORTS = (
     "dsdpa_status_string",
     "dsdpa_version",
     "dsdpa_last_cuda_error",
+    "dsdpa_kernel_launches",
     "dsdpa_device_error",
     "dsdpa_describe_plan",
     "dsdpa_probe_l2_read_bandwidth",
@@ -90,6 +91,8 @@ def lib() -> ctypes.CDLL:
     L.dsdpa_version.restype = ci
     L.dsdpa_last_cuda_error.argtypes = []
     L.dsdpa_last_cuda_error.restype = ci
+    L.dsdpa_kernel_launches.argtypes = []
+    L.dsdpa_kernel_launches.restype = ctypes.c_ulonglong
     L.dsdpa_device_error.argtypes = [ci]
     L.dsdpa_device_error.restype = ci
     L.dsdpa_describe_plan.argtypes = [pp, ctypes.c_char_p, ctypes.c_size_t]

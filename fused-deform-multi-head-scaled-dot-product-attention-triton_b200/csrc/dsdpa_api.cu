@@ -3,6 +3,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <atomic>
 
 #include "dsdpa_launch.cuh"
 
@@ -12,6 +13,7 @@ namespace dsdpa {
 __device__ int g_error_word;
 
 static thread_local int t_last_cuda_error = 0;
+static std::atomic<unsigned long long> g_launches{0};
 
 static int cuda_fail(cudaError_t e) {
     t_last_cuda_error = (int)e;
@@ -219,6 +221,8 @@ int dsdpa_version(void) { return DSDPA_VERSION; }
 
 int dsdpa_last_cuda_error(void) { return t_last_cuda_error; }
 
+unsigned long long dsdpa_kernel_launches(void) { return g_launches.load(); }
+
 int dsdpa_describe_plan(const dsdpa_problem* p, char* text, size_t cap) {
     int st = validate_problem(p);
     if (st != DSDPA_OK) return st;
@@ -264,7 +268,9 @@ int dsdpa_forward(const dsdpa_problem* p, const void* q, const void* k, const vo
         case DSDPA_BF16: e = launch_forward<__nv_bfloat16>(fp, plan, p->D, s); break;
         default: e = launch_forward<__half>(fp, plan, p->D, s); break;
     }
-    return e == cudaSuccess ? DSDPA_OK : cuda_fail(e);
+    if (e != cudaSuccess) return cuda_fail(e);
+    g_launches += 1;
+    return DSDPA_OK;
 }
 
 size_t dsdpa_backward_workspace_bytes(const dsdpa_problem* p) {
@@ -321,6 +327,7 @@ int dsdpa_backward(const dsdpa_problem* p, const void* q, const void* k, const v
         default: e = launch_backward_scatter<__half>(bp, plan, p->D, s); break;
     }
     if (e != cudaSuccess) return cuda_fail(e);
+    g_launches += p->dtype == DSDPA_F32 ? 1 : 3;
     if (p->dtype == DSDPA_BF16) {
         if ((e = launch_cast_from_f32<__nv_bfloat16>(dk32, dk, n, s)) != cudaSuccess) return cuda_fail(e);
         if ((e = launch_cast_from_f32<__nv_bfloat16>(dv32, dv, n, s)) != cudaSuccess) return cuda_fail(e);

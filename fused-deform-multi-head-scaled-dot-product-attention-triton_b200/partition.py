@@ -1,0 +1,127 @@
+"""(batch, head) partitioner: shards the operator over the GPUs of one box.
+
+The reference has no multi-device code.  Every (batch, head) slice of the operator is
+independent -- it reads only ``q, k, v[b, :, h]`` and ``coords[b]`` and writes only
+``out/dq/dk/dv[b, :, h]`` (reference ops/triton.py:47-51, 97, 246-257) -- so the work is
+split with no communication on the compute path; the only exchange is the final
+gather of the outputs onto one rank.
+
+Batch is split first: with the [B, V, Hh, L, D] layout a batch shard of every tensor
+(coordinates included) is one contiguous block.  Heads are split only when there are
+fewer batch elements than ranks; a head shard needs the whole coords[b].
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass(frozen=True)
+class Shard:
+    """Half-open ranges of batch elements and heads owned by one rank."""
+    b0: int
+    b1: int
+    h0: int
+    h1: int
+
+    @property
+    def empty(self) -> bool:
+        return self.b1 <= self.b0 or self.h1 <= self.h0
+
+    def units(self) -> int:
+        return max(0, self.b1 - self.b0) * max(0, self.h1 - self.h0)
+
+
+def _split(n: int, parts: int) -> List[range]:
+    base, extra = divmod(n, parts)
+    out, lo = [], 0
+    for i in range(parts):
+        hi = lo + base + (1 if i < extra else 0)
+        out.append(range(lo, hi))
+        lo = hi
+    return out
+
+
+def shard_plan(B: int, Hh: int, world: int) -> List[Shard]:
+    """One Shard per rank.  Batch-major; heads are split only when B < world."""
+    if B <= 0 or Hh <= 0 or world <= 0:
+        raise ValueError("B, Hh and world must be positive")
+    if B >= world:
+        return [Shard(r.start, r.stop, 0, Hh) for r in _split(B, world)]
+    # fewer batch elements than ranks: give each batch element a group of ranks that
+    # split its heads
+    groups = _split(world, B)          # ranks per batch element
+    plan: List[Optional[Shard]] = [None] * world
+    for b, ranks in enumerate(groups):
+        heads = _split(Hh, len(ranks))
+        for r, hr in zip(ranks, heads):
+            plan[r] = Shard(b, b + 1, hr.start, hr.stop)
+    return [s if s is not None else Shard(0, 0, 0, 0) for s in plan]
+
+
+def slice_inputs(shard: Shard, q, k, v, coords, *more):
+    """Views of the full tensors for one shard ([B, V, Hh, L, D] and coords [B, ...])."""
+    sl = (slice(shard.b0, shard.b1), slice(None), slice(shard.h0, shard.h1))
+    extra = tuple(t[sl] if t is not None else None for t in more)
+    return (q[sl], k[sl], v[sl], coords[shard.b0:shard.b1]) + extra
+
+
+def gather_to_root(local: torch.Tensor, plan: Sequence[Shard], full_shape, root: int = 0,
+                   group=None) -> Optional[torch.Tensor]:
+    """Gather every rank's ``[b, V, h, L, D]`` shard into the full tensor on ``root``.
+
+    Returns the full tensor on ``root`` and ``None`` elsewhere.  Equal batch shards go
+    through one ``dist.gather`` straight into views of the preallocated result (batch
+    shards are contiguous blocks of it); anything else uses point-to-point copies.
+    """
+    rank = dist.get_rank(group)
+    world = dist.get_world_size(group)
+    if len(plan) != world:
+        raise ValueError("plan does not match the process group")
+    full = None
+    if rank == root:
+        full = torch.empty(full_shape, dtype=local.dtype, device=local.device)
+    Hh = full_shape[2]
+    batch_only = all(s.h0 == 0 and s.h1 == Hh for s in plan)
+    equal = batch_only and len({s.b1 - s.b0 for s in plan}) == 1
+    local = local.contiguous()
+    if equal:
+        views = [full[s.b0:s.b1] for s in plan] if rank == root else None
+        dist.gather(local, views, dst=root, group=group)
+        return full
+    if rank == root:
+        reqs = []
+        staging = []
+        for r, s in enumerate(plan):
+            if s.empty:
+                continue
+            dst = full[s.b0:s.b1, :, s.h0:s.h1]
+            if r == root:
+                dst.copy_(local)
+                continue
+            if dst.is_contiguous():
+                reqs.append(dist.irecv(dst, src=r, group=group))
+            else:
+                tmp = torch.empty(dst.shape, dtype=dst.dtype, device=dst.device)
+                staging.append((dst, tmp))
+                reqs.append(dist.irecv(tmp, src=r, group=group))
+        for req in reqs:
+            req.wait()
+        for dst, tmp in staging:
+            dst.copy_(tmp)
+        return full
+    if not plan[rank].empty:
+        dist.send(local, dst=root, group=group)
+    return None
+
+
+def run_sharded(fn: Callable, q, k, v, coords, *, plan: Sequence[Shard], rank: int):
+    """Apply ``fn(q, k, v, coords)`` to this rank's shard of full-size inputs."""
+    s = plan[rank]
+    if s.empty:
+        return None
+    qs, ks, vs, cs = slice_inputs(s, q, k, v, coords)
+    return fn(qs.contiguous(), ks.contiguous(), vs.contiguous(), cs.contiguous())

@@ -108,6 +108,9 @@ const char* dsdpa_status_string(int status);
 /* DSDPA_VERSION of the loaded library. */
 int dsdpa_version(void);
 
+/* Kernels of this library launched by this process so far (memsets are not counted). */
+unsigned long long dsdpa_kernel_launches(void);
+
 /* cudaError_t value of the last failed CUDA call of this thread's last DSDPA_ERR_CUDA. */
 int dsdpa_last_cuda_error(void);
 
