@@ -47,7 +47,7 @@ int validate_problem(const dsdpa_problem* p) {
     return DSDPA_OK;
 }
 
-TilePlan plan_tiles(const dsdpa_problem& p, bool backward) {
+TilePlan plan_tiles(const dsdpa_problem& p, bool backward, bool allow_priv) {
     const int L = p.W * p.H, VL = p.V * L;
     const long long map_bytes = (long long)L * p.D * dtype_size(p.dtype);
     const long long acc_bytes = (long long)L * p.D * 4;
@@ -68,7 +68,8 @@ TilePlan plan_tiles(const dsdpa_problem& p, bool backward) {
     const bool can_stage = !(p.flags & DSDPA_FLAG_MAPS_FROM_L2) && smem_need(1, 4, false) <= kPlanSmemMax &&
                            2 * map_bytes < (1ll << 20);
     if (can_stage) {
-        const bool want_priv = backward && !(p.flags & DSDPA_FLAG_SCATTER_GLOBAL) && smem_need(1, 8, true) <= kPlanSmemMax;
+        const bool want_priv = backward && allow_priv && !(p.flags & DSDPA_FLAG_SCATTER_GLOBAL) &&
+                               smem_need(1, 8, true) <= kPlanSmemMax;
         double best_cost = 1e300;
         const int nqs_fwd[3] = { 4, 2, 1 }, nqs_bwd[2] = { 4, 1 };
         const int* nqs = backward ? nqs_bwd : nqs_fwd;
@@ -123,6 +124,43 @@ TilePlan plan_tiles(const dsdpa_problem& p, bool backward) {
     best.smem = (size_t)nw * kPlanRecBytesPerWarp + 16;
     best.ctas = (long long)p.B * p.Hh * best.tiles;
     return best;
+}
+
+GatherPlan plan_gather(const dsdpa_problem& p) {
+    GatherPlan g{};
+    const int L = p.W * p.H;
+    const long long rowb = (long long)p.D * dtype_size(p.dtype);
+    const long long per_query = 2 * rowb + (long long)p.S * 8;
+    long long qb_max = (kPlanSmemMax - 64) / per_query;
+    qb_max &= ~1ll;  // even, so that every tile's scalars start on a 16-byte boundary
+    if (qb_max > 65534) qb_max = 65534;
+    const size_t index_smem = ((size_t)8 * L + 256) * sizeof(int);
+    if (qb_max < 2 || p.S > 65535 || index_smem > (size_t)kPlanSmemMax) return g;  // ok = false
+    const int force_qb = env_int("DSDPA_GATHER_QB", 0);
+    if (force_qb >= 2 && force_qb <= qb_max) qb_max = force_qb & ~1;
+    g.tpv = (int)((L + qb_max - 1) / qb_max);
+    int qb = (L + g.tpv - 1) / g.tpv;
+    qb += qb & 1;
+    g.QB = qb;
+    g.ok = true;
+    g.gather_threads = 512;
+    g.gather_smem = (size_t)qb * 2 * rowb + (((size_t)qb * p.S * 8 + 15) & ~(size_t)15) + 16;
+    g.gather_ctas = (long long)p.B * p.Hh * p.V;
+    const long long T = (long long)p.V * g.tpv;
+    g.segments = (long long)p.B * T * p.V;
+    g.index_smem = index_smem;
+    g.scal_bytes = (((size_t)p.B * p.Hh * T * p.V * qb * p.S * 8) + 16 + 255) & ~(size_t)255;
+    g.entries_bytes = (((size_t)g.segments * qb * p.S * 4 * 8) + 255) & ~(size_t)255;
+    g.rowptr_bytes = (((size_t)g.segments * (L + 1) * 4) + 255) & ~(size_t)255;
+    return g;
+}
+
+// Which backward form a problem runs with.
+static bool use_two_pass(const dsdpa_problem& p, const GatherPlan& g) {
+    if (!g.ok) return false;
+    if (p.flags & (DSDPA_FLAG_SCATTER | DSDPA_FLAG_SCATTER_GLOBAL)) return false;
+    if (p.flags & DSDPA_FLAG_DETERMINISTIC) return true;
+    return env_int("DSDPA_BWD_TWO_PASS", 1) != 0;
 }
 
 static bool misaligned(const void* p) { return ((uintptr_t)p & 15u) != 0; }
@@ -227,13 +265,19 @@ int dsdpa_describe_plan(const dsdpa_problem* p, char* text, size_t cap) {
     int st = validate_problem(p);
     if (st != DSDPA_OK) return st;
     if (!text || cap == 0) return DSDPA_ERR_NULL_POINTER;
-    const TilePlan f = plan_tiles(*p, false), b = plan_tiles(*p, true);
+    const GatherPlan g = plan_gather(*p);
+    const bool two = use_two_pass(*p, g);
+    const TilePlan f = plan_tiles(*p, false, false), b = plan_tiles(*p, true, !two);
+    char tail[160] = "";
+    if (two)
+        std::snprintf(tail, sizeof tail, " bwd_gather[tpv=%d QB=%d ctas=%lld smem=%zu segments=%lld]", g.tpv, g.QB,
+                      g.gather_ctas, g.gather_smem, g.segments);
     std::snprintf(text, cap,
                   "fwd[%s nstage=%d nw=%d nq=%d tiles=%d q_per_tile=%d ctas=%lld smem=%zu] "
-                  "bwd_scatter[%s%s nstage=%d nw=%d nq=%d tiles=%d q_per_tile=%d ctas=%lld smem=%zu]",
+                  "bwd_%s[%s%s nstage=%d nw=%d nq=%d tiles=%d q_per_tile=%d ctas=%lld smem=%zu]%s",
                   f.staged ? "staged" : "l2", f.nstage, f.nw, f.nq, f.tiles, f.q_per_tile, f.ctas, f.smem,
-                  b.staged ? "staged" : "l2", b.priv ? "+priv" : "", b.nstage, b.nw, b.nq, b.tiles, b.q_per_tile,
-                  b.ctas, b.smem);
+                  two ? "pass_a" : "scatter", b.staged ? "staged" : "l2", b.priv ? "+priv" : "", b.nstage, b.nw, b.nq,
+                  b.tiles, b.q_per_tile, b.ctas, b.smem, tail);
     return DSDPA_OK;
 }
 
@@ -250,7 +294,7 @@ int dsdpa_forward(const dsdpa_problem* p, const void* q, const void* k, const vo
     cudaError_t e = error_word_ptr(device, &err_word);
     if (e != cudaSuccess) return cuda_fail(e);
 
-    const TilePlan plan = plan_tiles(*p, false);
+    const TilePlan plan = plan_tiles(*p, false, false);
     FwdParams fp{};
     fp.q = q; fp.k = k; fp.v = v; fp.coords = coords; fp.out = out; fp.lse = lse;
     fp.B = p->B; fp.V = p->V; fp.Hh = p->Hh; fp.W = p->W; fp.H = p->H; fp.L = p->W * p->H; fp.S = p->S;
@@ -277,7 +321,10 @@ size_t dsdpa_backward_workspace_bytes(const dsdpa_problem* p) {
     if (validate_problem(p) != DSDPA_OK) return 0;
     const size_t n = (size_t)p->B * p->V * p->Hh * p->W * p->H * p->D;
     // fp32 storage accumulates dK/dV in the outputs themselves
-    return p->dtype == DSDPA_F32 ? 0 : 2 * n * sizeof(float);
+    size_t bytes = p->dtype == DSDPA_F32 ? 0 : ((2 * n * sizeof(float) + 255) & ~(size_t)255);
+    const GatherPlan g = plan_gather(*p);
+    if (use_two_pass(*p, g)) bytes += g.scal_bytes + g.entries_bytes + g.rowptr_bytes;
+    return bytes;
 }
 
 int dsdpa_backward(const dsdpa_problem* p, const void* q, const void* k, const void* v, const float* coords,
@@ -300,40 +347,84 @@ int dsdpa_backward(const dsdpa_problem* p, const void* q, const void* k, const v
     if (e != cudaSuccess) return cuda_fail(e);
     cudaStream_t s = (cudaStream_t)stream;
 
+    const GatherPlan gp = plan_gather(*p);
+    const bool two_pass = use_two_pass(*p, gp);
     const size_t n = (size_t)p->B * p->V * p->Hh * p->W * p->H * p->D;
+    const size_t acc_bytes = p->dtype == DSDPA_F32 ? 0 : ((2 * n * sizeof(float) + 255) & ~(size_t)255);
     float* dk32 = p->dtype == DSDPA_F32 ? (float*)dk : (float*)workspace;
     float* dv32 = p->dtype == DSDPA_F32 ? (float*)dv : (float*)workspace + n;
     if ((e = cudaMemsetAsync(dk32, 0, n * sizeof(float), s)) != cudaSuccess) return cuda_fail(e);
     if ((e = cudaMemsetAsync(dv32, 0, n * sizeof(float), s)) != cudaSuccess) return cuda_fail(e);
 
-    const TilePlan plan = plan_tiles(*p, true);
+    const int L = p->W * p->H;
+    const float hw = (float)(p->W - 1) * 0.5f, hh = (float)(p->H - 1) * 0.5f;
+    char* ws = (char*)workspace + acc_bytes;
+    float2* scal = two_pass ? (float2*)ws : nullptr;
+    uint2* entries = two_pass ? (uint2*)(ws + gp.scal_bytes) : nullptr;
+    int* rowptr = two_pass ? (int*)(ws + gp.scal_bytes + gp.entries_bytes) : nullptr;
+
+    if (two_pass) {
+        // pixel-sorted sample lists, shared by all heads
+        IndexParams ip{};
+        ip.coords = coords; ip.rowptr = rowptr; ip.entries = entries;
+        ip.B = p->B; ip.V = p->V; ip.W = p->W; ip.H = p->H; ip.L = L; ip.S = p->S;
+        ip.hw = hw; ip.hh = hh; ip.tpv = gp.tpv; ip.QB = gp.QB;
+        static bool index_attr[64] = {};
+        if ((e = detail::allow_big_smem(index_build_kernel<kIndexWarpsDefault>, index_attr)) != cudaSuccess) return cuda_fail(e);
+        index_build_kernel<kIndexWarpsDefault><<<(unsigned)gp.segments, kIndexWarpsDefault * 32, gp.index_smem, s>>>(ip);
+        if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail(e);
+        g_launches += 1;
+    }
+
+    const TilePlan plan = plan_tiles(*p, true, !two_pass);
     BwdParams bp{};
     bp.q = q; bp.k = k; bp.v = v; bp.coords = coords; bp.out = out; bp.lse = lse; bp.dout = dout;
     bp.dq = dq; bp.dk32 = dk32; bp.dv32 = dv32; bp.dcoords = dcoords;
-    bp.B = p->B; bp.V = p->V; bp.Hh = p->Hh; bp.W = p->W; bp.H = p->H; bp.L = p->W * p->H; bp.S = p->S;
+    bp.B = p->B; bp.V = p->V; bp.Hh = p->Hh; bp.W = p->W; bp.H = p->H; bp.L = L; bp.S = p->S;
     bp.sm_scale = p->sm_scale;
     bp.scale2 = p->sm_scale * kLog2e;
-    bp.hw = (float)(p->W - 1) * 0.5f;
-    bp.hh = (float)(p->H - 1) * 0.5f;
+    bp.hw = hw;
+    bp.hh = hh;
     bp.tiles = plan.tiles;
     bp.q_per_tile = plan.q_per_tile;
     bp.nstage = plan.nstage;
-    bp.map_bytes = (unsigned)((size_t)bp.L * p->D * dtype_size(p->dtype));
-    bp.acc_bytes = (unsigned)((size_t)bp.L * p->D * 4);
+    bp.map_bytes = (unsigned)((size_t)L * p->D * dtype_size(p->dtype));
+    bp.acc_bytes = (unsigned)((size_t)L * p->D * 4);
     bp.err = err_word;
+    bp.scal = scal;
+    bp.tpv = gp.tpv;
+    bp.QB = gp.QB;
     switch (p->dtype) {
-        case DSDPA_F32: e = launch_backward_scatter<float>(bp, plan, p->D, s); break;
-        case DSDPA_BF16: e = launch_backward_scatter<__nv_bfloat16>(bp, plan, p->D, s); break;
-        default: e = launch_backward_scatter<__half>(bp, plan, p->D, s); break;
+        case DSDPA_F32: e = launch_backward_main<float>(bp, plan, p->D, two_pass, s); break;
+        case DSDPA_BF16: e = launch_backward_main<__nv_bfloat16>(bp, plan, p->D, two_pass, s); break;
+        default: e = launch_backward_main<__half>(bp, plan, p->D, two_pass, s); break;
     }
     if (e != cudaSuccess) return cuda_fail(e);
-    g_launches += p->dtype == DSDPA_F32 ? 1 : 3;
+    g_launches += 1;
+
+    if (two_pass) {
+        GatherParams g{};
+        g.q = q; g.dout = dout; g.scal = scal; g.rowptr = rowptr; g.entries = entries;
+        g.dk32 = dk32; g.dv32 = dv32;
+        g.B = p->B; g.V = p->V; g.Hh = p->Hh; g.L = L; g.S = p->S; g.tpv = gp.tpv; g.QB = gp.QB;
+        g.err = err_word;
+        switch (p->dtype) {
+            case DSDPA_F32: e = launch_backward_gather<float>(g, gp, p->D, s); break;
+            case DSDPA_BF16: e = launch_backward_gather<__nv_bfloat16>(g, gp, p->D, s); break;
+            default: e = launch_backward_gather<__half>(g, gp, p->D, s); break;
+        }
+        if (e != cudaSuccess) return cuda_fail(e);
+        g_launches += 1;
+    }
+
     if (p->dtype == DSDPA_BF16) {
         if ((e = launch_cast_from_f32<__nv_bfloat16>(dk32, dk, n, s)) != cudaSuccess) return cuda_fail(e);
         if ((e = launch_cast_from_f32<__nv_bfloat16>(dv32, dv, n, s)) != cudaSuccess) return cuda_fail(e);
+        g_launches += 2;
     } else if (p->dtype == DSDPA_F16) {
         if ((e = launch_cast_from_f32<__half>(dk32, dk, n, s)) != cudaSuccess) return cuda_fail(e);
         if ((e = launch_cast_from_f32<__half>(dv32, dv, n, s)) != cudaSuccess) return cuda_fail(e);
+        g_launches += 2;
     }
     return DSDPA_OK;
 }

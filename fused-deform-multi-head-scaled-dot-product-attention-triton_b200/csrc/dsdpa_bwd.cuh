@@ -43,11 +43,19 @@ struct BwdParams {
     unsigned map_bytes;   // bytes of one [L, D] map in the storage type
     unsigned acc_bytes;   // bytes of one [L, D] fp32 map (PRIV)
     int* err;             // device error word
+    // two-pass form: per-sample scalars (sm_scale*ds, p) for the gather pass, laid out
+    // [B, Hh, V*tpv tiles, V key views, QB queries, S] as float2
+    float2* scal;
+    int tpv;              // gather-pass tiles per query view
+    int QB;               // queries per gather-pass tile
 };
 
-template <typename T, int D, int NQ, bool STAGED, bool PRIV, int MAXT, int MINB>
+// TWOPASS: no scatter; instead every sample's (sm_scale*ds, p) is written out for the
+// gather pass (bwd_gather_kernel) that forms dK/dV without atomics.
+template <typename T, int D, int NQ, bool STAGED, bool PRIV, bool TWOPASS, int MAXT, int MINB>
 __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams p) {
     static_assert(!PRIV || STAGED, "privatised accumulators live next to staged maps");
+    static_assert(!(PRIV && TWOPASS), "the two-pass form has nothing to privatise");
     using RC = RowCfg<T, D>;
     constexpr int G = RC::G, NG = RC::NG, EPL = RC::EPL, CH = RC::CH, EPV = RC::EPV, ROWB = RC::ROWB;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -171,7 +179,14 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
                 const float2* cptr = reinterpret_cast<const float2*>(p.coords) +
                                      ((((size_t)b * p.V + vq) * p.L + l) * p.V + vk) * (size_t)p.S;
                 const float lse = lse_q[j], delta = delta_q[j];
+                float2* scal_row = nullptr;
+                if constexpr (TWOPASS) {
+                    const int tl = l / p.QB, ql = l - tl * p.QB;
+                    const size_t tile = ((size_t)b * p.Hh + h) * (size_t)(p.V * p.tpv) + (size_t)(vq * p.tpv + tl);
+                    scal_row = p.scal + ((tile * p.V + vk) * (size_t)p.QB + ql) * (size_t)p.S;
+                }
                 for (int s0 = 0; s0 < p.S; s0 += G) {
+                    float my_a = 0.0f, my_p = 0.0f;  // TWOPASS: scalars of sample s0+li
                     {
                         const int s = s0 + li;
                         float2 c = make_float2(0.0f, 0.0f);
@@ -208,10 +223,17 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
                         const float ds = pe * (dp - delta);
 #pragma unroll
                         for (int e = 0; e < EPL; ++e) dq[j][e] = fmaf(ds, kt[e], dq[j][e]);
+                        if constexpr (TWOPASS) {
+                            if (i == li) {
+                                my_a = ds * p.sm_scale;
+                                my_p = pe;
+                            }
+                        }
                         // qf carries scale2 = sm_scale*log2(e): sm_scale*ds*q = (ds*ln2)*qf
                         const float ck = ds * kLn2;
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
+                            if constexpr (TWOPASS) continue;
                             if (!live || w[c] == 0.0f) continue;
                             const float wk = ck * w[c], wv = pe * w[c];
 #pragma unroll
@@ -236,6 +258,10 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
                                 }
                             }
                         }
+                    }
+                    if constexpr (TWOPASS) {
+                        // one coalesced float2 per lane: the group writes G samples at once
+                        if (live && li < cnt) scal_row[s0 + li] = make_float2(my_a, my_p);
                     }
                     __syncwarp();
                 }

@@ -5,14 +5,18 @@
 #pragma once
 
 #include "dsdpa_bwd.cuh"
+#include "dsdpa_bwd2.cuh"
 #include "dsdpa_plan.h"
 
 namespace dsdpa {
 
 template <typename T>
 cudaError_t launch_forward(const FwdParams& p, const TilePlan& plan, int D, cudaStream_t stream);
+// two_pass: the kernel writes per-sample scalars instead of scattering (pass A)
 template <typename T>
-cudaError_t launch_backward_scatter(const BwdParams& p, const TilePlan& plan, int D, cudaStream_t stream);
+cudaError_t launch_backward_main(const BwdParams& p, const TilePlan& plan, int D, bool two_pass, cudaStream_t stream);
+template <typename T>
+cudaError_t launch_backward_gather(const GatherParams& p, const GatherPlan& plan, int D, cudaStream_t stream);
 template <typename T>
 cudaError_t launch_cast_from_f32(const float* src, void* dst, size_t n, cudaStream_t stream);
 
@@ -57,10 +61,11 @@ inline cudaError_t fwd_d(const FwdParams& p, const TilePlan& plan, cudaStream_t 
     }
 }
 
-template <typename T, int D, int NQ, bool STAGED, bool PRIV>
+template <typename T, int D, int NQ, bool STAGED, bool PRIV, bool TWOPASS>
 inline cudaError_t bwd_one(const BwdParams& p, const TilePlan& plan, cudaStream_t stream) {
-    auto kern = bwd_scatter_kernel<T, D, NQ, STAGED, PRIV, STAGED ? kStagedMaxThreads : kL2MaxThreads, STAGED ? 1 : 2>;
-    static bool done[64] = {};  // a benign race at worst repeats the attribute call
+    auto kern = bwd_scatter_kernel<T, D, NQ, STAGED, PRIV, TWOPASS, STAGED ? kStagedMaxThreads : kL2MaxThreads,
+                                   STAGED ? 1 : 2>;
+    static bool done[64] = {};
     cudaError_t e = allow_big_smem(kern, done);
     if (e != cudaSuccess) return e;
     kern<<<(unsigned)plan.ctas, plan.nw * 32, plan.smem, stream>>>(p);
@@ -68,20 +73,39 @@ inline cudaError_t bwd_one(const BwdParams& p, const TilePlan& plan, cudaStream_
 }
 
 template <typename T, int D>
-inline cudaError_t bwd_d(const BwdParams& p, const TilePlan& plan, cudaStream_t stream) {
-    if (!plan.staged) return bwd_one<T, D, 1, false, false>(p, plan, stream);
+inline cudaError_t bwd_d(const BwdParams& p, const TilePlan& plan, bool two_pass, cudaStream_t stream) {
+    if (two_pass) {
+        if (plan.priv) return cudaErrorInvalidValue;
+        if (!plan.staged) return bwd_one<T, D, 1, false, false, true>(p, plan, stream);
+        switch (plan.nq) {
+            case 1: return bwd_one<T, D, 1, true, false, true>(p, plan, stream);
+            case 4: return bwd_one<T, D, 4, true, false, true>(p, plan, stream);
+            default: return cudaErrorInvalidValue;
+        }
+    }
+    if (!plan.staged) return bwd_one<T, D, 1, false, false, false>(p, plan, stream);
     if (plan.priv) {
         switch (plan.nq) {
-            case 1: return bwd_one<T, D, 1, true, true>(p, plan, stream);
-            case 4: return bwd_one<T, D, 4, true, true>(p, plan, stream);
+            case 1: return bwd_one<T, D, 1, true, true, false>(p, plan, stream);
+            case 4: return bwd_one<T, D, 4, true, true, false>(p, plan, stream);
             default: return cudaErrorInvalidValue;
         }
     }
     switch (plan.nq) {
-        case 1: return bwd_one<T, D, 1, true, false>(p, plan, stream);
-        case 4: return bwd_one<T, D, 4, true, false>(p, plan, stream);
+        case 1: return bwd_one<T, D, 1, true, false, false>(p, plan, stream);
+        case 4: return bwd_one<T, D, 4, true, false, false>(p, plan, stream);
         default: return cudaErrorInvalidValue;
     }
+}
+
+template <typename T, int D>
+inline cudaError_t gather_d(const GatherParams& p, const GatherPlan& plan, cudaStream_t stream) {
+    auto kern = bwd_gather_kernel<T, D>;
+    static bool done[64] = {};
+    cudaError_t e = allow_big_smem(kern, done);
+    if (e != cudaSuccess) return e;
+    kern<<<(unsigned)plan.gather_ctas, plan.gather_threads, plan.gather_smem, stream>>>(p);
+    return cudaGetLastError();
 }
 
 }  // namespace detail

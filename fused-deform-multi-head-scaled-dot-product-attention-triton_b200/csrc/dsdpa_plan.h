@@ -40,11 +40,26 @@ struct TilePlan {
     long long ctas;
 };
 
+// Two-pass backward: gather tiles and the layout of its scratch inside the workspace.
+struct GatherPlan {
+    bool ok;            // the shape can run the two-pass form
+    int tpv;            // gather tiles per query view
+    int QB;             // queries (pixels of one query view) per gather tile, even
+    int gather_threads;
+    size_t gather_smem;
+    long long gather_ctas;   // B*Hh*V
+    long long segments;      // B * (V*tpv) * V index segments
+    size_t index_smem;
+    // byte offsets inside the workspace (after the fp32 dK/dV accumulators, if any)
+    size_t scal_bytes, entries_bytes, rowptr_bytes;
+};
+GatherPlan plan_gather(const dsdpa_problem& p);
+
 // Environment overrides for experiments: DSDPA_<which>_NW, DSDPA_<which>_NQ.
 int env_int(const char* name, int fallback);
 
 // `backward`: plan for the scatter kernel (it can additionally privatise dK/dV).
-TilePlan plan_tiles(const dsdpa_problem& p, bool backward);
+TilePlan plan_tiles(const dsdpa_problem& p, bool backward, bool allow_priv);
 
 int validate_problem(const dsdpa_problem* p);
 

@@ -32,9 +32,12 @@ def _run(backend, case_or_tensors, flags, dtype, W, H, sm_scale):
 
 
 FLAG_SETS = {
-    "default": 0,
+    "default": 0,                 # two-pass backward where the shape allows it
     "maps_from_l2": 0x1,
-    "scatter_global": 0x4,
+    "deterministic": 0x2,
+    "scatter": 0x8,               # one-kernel scatter, shared-memory privatised where it fits
+    "scatter_global": 0x4,        # one-kernel scatter, reductions straight to global memory
+    "scatter_maps_from_l2": 0x9,
 }
 
 
@@ -91,3 +94,15 @@ def test_configs_against_oracle(backend, oracle, cfgname):
     print(cfgname, {n: f"{e:.2e}" for n, e in errs.items()})
     for n, e in errs.items():
         assert e < tol, (n, e)
+
+
+def test_two_pass_backward_is_bit_reproducible(backend):
+    """The two-pass dK/dV sums every pixel's contributions in a fixed order: two runs on the
+    same inputs agree bit for bit (the scatter forms, built on floating-point atomics, do not
+    promise that)."""
+    cfg = backend.inputs.CONFIGS["C2"]
+    q, k, v, coords, dout = backend.inputs.make_inputs(cfg)
+    a = _run(backend, (q, k, v, coords, dout), 0x2, cfg.dtype, cfg.W, cfg.H, cfg.sm_scale)
+    b = _run(backend, (q, k, v, coords, dout), 0x2, cfg.dtype, cfg.W, cfg.H, cfg.sm_scale)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
