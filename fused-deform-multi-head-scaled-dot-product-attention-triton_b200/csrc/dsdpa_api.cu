@@ -77,7 +77,8 @@ TilePlan plan_tiles(const dsdpa_problem& p, bool backward, bool allow_priv) {
         for (int qi = 0; qi < n_nq; ++qi) {
             const int nq = nqs[qi];
             if (force_nq && nq != force_nq) continue;
-            for (int nw = 16; nw >= 4; nw -= 2) {
+            // multiples of four warps keep the four schedulers of an SM evenly loaded
+            for (int nw = 16; nw >= 4; nw -= 4) {
                 if (force_nw && nw != force_nw) continue;
                 if (smem_need(1, nw, want_priv) > kPlanSmemMax) continue;
                 const int nstage = smem_need(2, nw, want_priv) <= kPlanSmemMax ? 2 : 1;
@@ -131,9 +132,11 @@ GatherPlan plan_gather(const dsdpa_problem& p) {
     const int L = p.W * p.H;
     const long long rowb = (long long)p.D * dtype_size(p.dtype);
     const long long per_query = 2 * rowb + (long long)p.S * 8;
-    long long qb_max = (kPlanSmemMax - 64) / per_query;
+    const long long budget = (long long)env_int("DSDPA_GATHER_SMEM_KB", 224) * 1024;
+    long long qb_max = ((budget < kPlanSmemMax ? budget : kPlanSmemMax) - 64) / per_query;
     qb_max &= ~1ll;  // even, so that every tile's scalars start on a 16-byte boundary
-    if (qb_max > 65534) qb_max = 65534;
+    // entries address a query's row in 16-byte units and a sample's scalars by index, 16 bits each
+    while (qb_max > 2 && (qb_max * rowb / 16 > 65535 || qb_max * p.S > 65535)) qb_max -= 2;
     const size_t index_smem = ((size_t)8 * L + 256) * sizeof(int);
     if (qb_max < 2 || p.S > 65535 || index_smem > (size_t)kPlanSmemMax) return g;  // ok = false
     const int force_qb = env_int("DSDPA_GATHER_QB", 0);
@@ -143,14 +146,16 @@ GatherPlan plan_gather(const dsdpa_problem& p) {
     qb += qb & 1;
     g.QB = qb;
     g.ok = true;
-    g.gather_threads = 512;
+    g.gather_threads = env_int("DSDPA_GATHER_THREADS", 768);
+    if (g.gather_threads < 32 || g.gather_threads > 768 || g.gather_threads % 32) g.gather_threads = 768;
     g.gather_smem = (size_t)qb * 2 * rowb + (((size_t)qb * p.S * 8 + 15) & ~(size_t)15) + 16;
     g.gather_ctas = (long long)p.B * p.Hh * p.V;
     const long long T = (long long)p.V * g.tpv;
     g.segments = (long long)p.B * T * p.V;
     g.index_smem = index_smem;
     g.scal_bytes = (((size_t)p.B * p.Hh * T * p.V * qb * p.S * 8) + 16 + 255) & ~(size_t)255;
-    g.entries_bytes = (((size_t)g.segments * qb * p.S * 4 * 8) + 255) & ~(size_t)255;
+    g.seg_entries = (int)(((long long)qb * p.S * 4 + 3ll * L + 3) & ~3ll);
+    g.entries_bytes = (((size_t)g.segments * g.seg_entries * 8) + 255) & ~(size_t)255;
     g.rowptr_bytes = (((size_t)g.segments * (L + 1) * 4) + 255) & ~(size_t)255;
     return g;
 }
@@ -369,6 +374,7 @@ int dsdpa_backward(const dsdpa_problem* p, const void* q, const void* k, const v
         ip.coords = coords; ip.rowptr = rowptr; ip.entries = entries;
         ip.B = p->B; ip.V = p->V; ip.W = p->W; ip.H = p->H; ip.L = L; ip.S = p->S;
         ip.hw = hw; ip.hh = hh; ip.tpv = gp.tpv; ip.QB = gp.QB;
+        ip.rowb16 = p->D * dtype_size(p->dtype) / 16; ip.seg_entries = gp.seg_entries;
         static bool index_attr[64] = {};
         if ((e = detail::allow_big_smem(index_build_kernel<kIndexWarpsDefault>, index_attr)) != cudaSuccess) return cuda_fail(e);
         index_build_kernel<kIndexWarpsDefault><<<(unsigned)gp.segments, kIndexWarpsDefault * 32, gp.index_smem, s>>>(ip);
@@ -407,6 +413,7 @@ int dsdpa_backward(const dsdpa_problem* p, const void* q, const void* k, const v
         g.q = q; g.dout = dout; g.scal = scal; g.rowptr = rowptr; g.entries = entries;
         g.dk32 = dk32; g.dv32 = dv32;
         g.B = p->B; g.V = p->V; g.Hh = p->Hh; g.L = L; g.S = p->S; g.tpv = gp.tpv; g.QB = gp.QB;
+        g.seg_entries = gp.seg_entries;
         g.err = err_word;
         switch (p->dtype) {
             case DSDPA_F32: e = launch_backward_gather<float>(g, gp, p->D, s); break;

@@ -58,6 +58,7 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
     static_assert(!(PRIV && TWOPASS), "the two-pass form has nothing to privatise");
     using RC = RowCfg<T, D>;
     constexpr int G = RC::G, NG = RC::NG, EPL = RC::EPL, CH = RC::CH, EPV = RC::EPV, ROWB = RC::ROWB;
+    constexpr int HP = EPL / 2, HV = EPV / 2;  // fp32 pairs per lane / per 16-byte vector
     extern __shared__ __align__(128) unsigned char smem[];
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -105,11 +106,12 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
     }
 
     // per-slot state that does not depend on the key view
-    float dq[NQ][EPL], lse_q[NQ], delta_q[NQ];
+    float2 dq[NQ][HP];
+    float lse_q[NQ], delta_q[NQ];
 #pragma unroll
     for (int j = 0; j < NQ; ++j) {
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) dq[j][e] = 0.0f;
+        for (int e = 0; e < HP; ++e) dq[j][e] = make_float2(0.0f, 0.0f);
         lse_q[j] = 0.0f;
         delta_q[j] = 0.0f;
         if (q0 + j * slot_stride + warp * NG >= qend) continue;
@@ -165,16 +167,16 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
                 const int qi = min(qslot, qend - 1);
                 const int vq = qi / p.L, l = qi - vq * p.L;
                 const size_t qrow = (((size_t)b * p.V + vq) * p.Hh + h) * p.L + l;
-                float qf[EPL], dof[EPL];
+                float2 qf[HP], dof[HP];
 #pragma unroll
                 for (int ch = 0; ch < CH; ++ch) {
-                    float f[EPV];
-                    unpack16(ldg128_nc((const char*)p.q + qrow * ROWB + (size_t)(ch * G + li) * 16), f, (T*)nullptr);
+                    float2 f[HV];
+                    unpack16_pairs(ldg128_nc((const char*)p.q + qrow * ROWB + (size_t)(ch * G + li) * 16), f, (T*)nullptr);
 #pragma unroll
-                    for (int e = 0; e < EPV; ++e) qf[ch * EPV + e] = f[e] * p.scale2;
-                    unpack16(ldg128_nc((const char*)p.dout + qrow * ROWB + (size_t)(ch * G + li) * 16), f, (T*)nullptr);
+                    for (int e = 0; e < HV; ++e) qf[ch * HV + e] = make_float2(f[e].x * p.scale2, f[e].y * p.scale2);
+                    unpack16_pairs(ldg128_nc((const char*)p.dout + qrow * ROWB + (size_t)(ch * G + li) * 16), f, (T*)nullptr);
 #pragma unroll
-                    for (int e = 0; e < EPV; ++e) dof[ch * EPV + e] = f[e];
+                    for (int e = 0; e < HV; ++e) dof[ch * HV + e] = f[e];
                 }
                 const float2* cptr = reinterpret_cast<const float2*>(p.coords) +
                                      ((((size_t)b * p.V + vq) * p.L + l) * p.V + vk) * (size_t)p.S;
@@ -187,42 +189,33 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
                 }
                 for (int s0 = 0; s0 < p.S; s0 += G) {
                     float my_a = 0.0f, my_p = 0.0f;  // TWOPASS: scalars of sample s0+li
-                    {
-                        const int s = s0 + li;
-                        float2 c = make_float2(0.0f, 0.0f);
-                        if (s < p.S) c = __ldg(cptr + s);
-                        Corners cr;
-                        float fx, fy;
-                        decode_corners(c.x, c.y, p.W, p.H, p.hw, p.hh, cr, fx, fy);
-                        const uint32_t r = (uint32_t)(li * NG + g) * 16u;
-                        sts128(rec_w + r, make_uint4(__float_as_uint(cr.w[0]), __float_as_uint(cr.w[1]),
-                                                     __float_as_uint(cr.w[2]), __float_as_uint(cr.w[3])));
-                        sts128(rec_p + r, make_uint4((uint32_t)cr.pix[0], (uint32_t)cr.pix[1],
-                                                     (uint32_t)cr.pix[2], (uint32_t)cr.pix[3]));
-                    }
+                    publish_record<G, NG>(cptr, s0 + li, p.S, p.W, p.H, p.hw, p.hh, rec_w, rec_p, li, g);
                     __syncwarp();
                     const int cnt = min(G, p.S - s0);
                     for (int i = 0; i < cnt; ++i) {
-                        const uint32_t r = (uint32_t)(i * NG + g) * 16u;
+                        const uint32_t r = rec_slot<G, NG>(i, g) * 16u;
                         const uint4 wr = lds128(rec_w + r), pr = lds128(rec_p + r);
                         const float w[4] = { __uint_as_float(wr.x), __uint_as_float(wr.y),
                                              __uint_as_float(wr.z), __uint_as_float(wr.w) };
+                        const float2 w2[4] = { make_float2(w[0], w[0]), make_float2(w[1], w[1]),
+                                               make_float2(w[2], w[2]), make_float2(w[3], w[3]) };
                         const int pix[4] = { (int)pr.x, (int)pr.y, (int)pr.z, (int)pr.w };
-                        float kt[EPL], vt[EPL];
-                        gather_interp<T, D, STAGED>(kmap, pix, w, li, kt);
-                        gather_interp<T, D, STAGED>(vmap, pix, w, li, vt);
-                        float ps = 0.0f, pd = 0.0f;
+                        float2 kt[HP], vt[HP];
+                        gather_interp<T, D, STAGED>(kmap, pix, w2, li, kt);
+                        gather_interp<T, D, STAGED>(vmap, pix, w2, li, vt);
+                        float2 ps = __fmul2_rn(qf[0], kt[0]), pd = __fmul2_rn(dof[0], vt[0]);
 #pragma unroll
-                        for (int e = 0; e < EPL; ++e) {
-                            ps = fmaf(qf[e], kt[e], ps);
-                            pd = fmaf(dof[e], vt[e], pd);
+                        for (int e = 1; e < HP; ++e) {
+                            ps = __ffma2_rn(qf[e], kt[e], ps);
+                            pd = __ffma2_rn(dof[e], vt[e], pd);
                         }
-                        const float sc = group_sum<G>(ps);
-                        const float dp = group_sum<G>(pd);
+                        const float sc = group_sum<G>(ps.x + ps.y);
+                        const float dp = group_sum<G>(pd.x + pd.y);
                         const float pe = fast_exp2(sc - lse);
                         const float ds = pe * (dp - delta);
+                        const float2 ds2 = make_float2(ds, ds);
 #pragma unroll
-                        for (int e = 0; e < EPL; ++e) dq[j][e] = fmaf(ds, kt[e], dq[j][e]);
+                        for (int e = 0; e < HP; ++e) dq[j][e] = __ffma2_rn(ds2, kt[e], dq[j][e]);
                         if constexpr (TWOPASS) {
                             if (i == li) {
                                 my_a = ds * p.sm_scale;
@@ -238,22 +231,24 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
                             const float wk = ck * w[c], wv = pe * w[c];
 #pragma unroll
                             for (int ch = 0; ch < CH; ++ch) {
-                                const int e0 = ch * EPV;
+                                const int h0 = ch * HV;
                                 const size_t off = (size_t)pix[c] * D + (size_t)(ch * G + li) * EPV;
                                 if constexpr (PRIV) {
                                     const uint32_t ak = acc_k + (uint32_t)off * 4u, av = acc_v + (uint32_t)off * 4u;
 #pragma unroll
-                                    for (int e = 0; e < EPV; ++e) {
-                                        red_shared_add(ak + 4u * e, wk * qf[e0 + e]);
-                                        red_shared_add(av + 4u * e, wv * dof[e0 + e]);
+                                    for (int e = 0; e < HV; ++e) {
+                                        red_shared_add(ak + 8u * e, wk * qf[h0 + e].x);
+                                        red_shared_add(ak + 8u * e + 4u, wk * qf[h0 + e].y);
+                                        red_shared_add(av + 8u * e, wv * dof[h0 + e].x);
+                                        red_shared_add(av + 8u * e + 4u, wv * dof[h0 + e].y);
                                     }
                                 } else {
 #pragma unroll
-                                    for (int e = 0; e < EPV; e += 4) {
-                                        red_global_add_v4(dkmap + off + e, wk * qf[e0 + e], wk * qf[e0 + e + 1],
-                                                          wk * qf[e0 + e + 2], wk * qf[e0 + e + 3]);
-                                        red_global_add_v4(dvmap + off + e, wv * dof[e0 + e], wv * dof[e0 + e + 1],
-                                                          wv * dof[e0 + e + 2], wv * dof[e0 + e + 3]);
+                                    for (int e = 0; e < HV; e += 2) {
+                                        red_global_add_v4(dkmap + off + 2 * e, wk * qf[h0 + e].x, wk * qf[h0 + e].y,
+                                                          wk * qf[h0 + e + 1].x, wk * qf[h0 + e + 1].y);
+                                        red_global_add_v4(dvmap + off + 2 * e, wv * dof[h0 + e].x, wv * dof[h0 + e].y,
+                                                          wv * dof[h0 + e + 1].x, wv * dof[h0 + e + 1].y);
                                     }
                                 }
                             }
@@ -302,7 +297,10 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
         for (int ch = 0; ch < CH; ++ch) {
             float f[EPV];
 #pragma unroll
-            for (int e = 0; e < EPV; ++e) f[e] = dq[j][ch * EPV + e] * p.sm_scale;
+            for (int e = 0; e < HV; ++e) {
+                f[2 * e] = dq[j][ch * HV + e].x * p.sm_scale;
+                f[2 * e + 1] = dq[j][ch * HV + e].y * p.sm_scale;
+            }
             stg128((char*)p.dq + qrow * ROWB + (size_t)(ch * G + li) * 16, pack16(f, (T*)nullptr));
         }
     }

@@ -7,8 +7,9 @@
 //   1. index_build_kernel   (per batch element, gather tile and key view; shared by all
 //      heads, since coordinates are, ops/torch.py:10): a counting sort of the tile's
 //      (sample, corner) pairs by key pixel.  Output per segment: row pointers [L+1] and
-//      entries {query-in-tile | sample<<16, weight}, each pixel's entries in a fixed
-//      canonical order.
+//      entries {row offset of the query in the tile | index of the sample's scalars << 16,
+//      weight}, each pixel's entries in a fixed canonical order and padded with zero-weight
+//      entries to a multiple of four (the gather pass reads four entries per step).
 //   2. bwd_scatter_kernel<..., TWOPASS>  (dsdpa_bwd.cuh): recomputes p and ds per sample,
 //      writes dq and the per-sample scalars (sm_scale*ds, p).
 //   3. bwd_gather_kernel    (per batch element, head and key view): for every gather tile
@@ -32,6 +33,8 @@ struct IndexParams {
     int B, V, W, H, L, S;
     float hw, hh;
     int tpv, QB;      // T = V*tpv tiles per batch element
+    int rowb16;       // bytes of one q row in the gather tile / 16
+    int seg_entries;  // entries reserved per segment (QB*S*4 + 3*L, rounded up to 4)
 };
 
 constexpr int kIndexWarpsDefault = 8;
@@ -92,8 +95,11 @@ __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexPar
     const int chunk = (p.L + nthr - 1) / nthr;
     const int pbeg = min((int)threadIdx.x * chunk, p.L), pend = min(pbeg + chunk, p.L);
     int local = 0;
-    for (int pix = pbeg; pix < pend; ++pix)
-        for (int w = 0; w < kIndexWarps; ++w) local += cnt[w * p.L + pix];
+    for (int pix = pbeg; pix < pend; ++pix) {
+        int tot = 0;
+        for (int w = 0; w < kIndexWarps; ++w) tot += cnt[w * p.L + pix];
+        local += (tot + 3) & ~3;  // every list is padded to a multiple of four entries
+    }
     part[threadIdx.x] = local;
     __syncthreads();
     if (warp == 0) {
@@ -116,11 +122,13 @@ __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexPar
     int run = part[threadIdx.x];
     for (int pix = pbeg; pix < pend; ++pix) {
         rowptr[pix] = run;
+        int at = run;
         for (int w = 0; w < kIndexWarps; ++w) {
             const int c = cnt[w * p.L + pix];
-            cnt[w * p.L + pix] = run;
-            run += c;
+            cnt[w * p.L + pix] = at;
+            at += c;
         }
+        run += (at - run + 3) & ~3;
     }
     if (pend == p.L && pbeg < p.L) rowptr[p.L] = run;
     if (p.L == 0 && threadIdx.x == 0) rowptr[0] = 0;
@@ -128,7 +136,7 @@ __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexPar
 
     // pass 3: scatter in canonical order (32 samples at a time, corner-major inside),
     // ranks of equal pixels inside the warp from match_any
-    uint2* entries = p.entries + (size_t)seg * ((size_t)p.QB * p.S * 4);
+    uint2* entries = p.entries + (size_t)seg * (size_t)p.seg_entries;
     for (int base = wbeg; base < wend; base += 32) {
         const int smp = base + lane;
         Corners cr;
@@ -139,8 +147,10 @@ __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexPar
             const float2 c = coord_of(smp);
             float fx, fy;
             decode_corners(c.x, c.y, p.W, p.H, p.hw, p.hh, cr, fx, fy);
-            const int ql = smp / p.S, s = smp - ql * p.S;
-            tag = (unsigned)ql | ((unsigned)s << 16);
+            const int ql = smp / p.S;
+            // what the gather pass needs of the sample: where its query's row starts in the tile
+            // (in 16-byte units) and which of the tile's scalar pairs is its own
+            tag = (unsigned)(ql * p.rowb16) | ((unsigned)smp << 16);
         }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -162,6 +172,13 @@ __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexPar
             __syncwarp();
         }
     }
+    __syncthreads();
+    // zero-weight padding behind every list (the last warp's cursor marks the list's end)
+    for (int pix = pbeg; pix < pend; ++pix) {
+        int at = cnt[(kIndexWarps - 1) * p.L + pix];
+        const int padded = (at + 3) & ~3;
+        for (; at < padded; ++at) entries[at] = make_uint2(0u, 0u);
+    }
 }
 
 struct GatherParams {
@@ -174,13 +191,17 @@ struct GatherParams {
     float* dv32;
     int B, V, Hh, L, S;
     int tpv, QB;
+    int seg_entries;
     int* err;
 };
 
+// Shared memory of one tile: q rows and dout rows in the storage type ([QB, D] each), then
+// the tile's scalars ([QB, S] float2), then the mbarrier; all three filled by bulk copies.
 template <typename T, int D>
-__global__ void __launch_bounds__(512, 1) bwd_gather_kernel(const GatherParams p) {
+__global__ void __launch_bounds__(768, 1) bwd_gather_kernel(const GatherParams p) {
     using RC = RowCfg<T, D>;
-    constexpr int G = RC::G, NG = RC::NG, EPL = RC::EPL, CH = RC::CH, EPV = RC::EPV, ROWB = RC::ROWB;
+    constexpr int G = RC::G, NG = RC::NG, CH = RC::CH, EPV = RC::EPV, ROWB = RC::ROWB;
+    constexpr int HV = EPV / 2, HP = RC::EPL / 2;
     extern __shared__ __align__(128) unsigned char smem[];
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -193,9 +214,9 @@ __global__ void __launch_bounds__(512, 1) bwd_gather_kernel(const GatherParams p
     const int NT = p.V * p.tpv;  // gather tiles per batch element
 
     const uint32_t smem0 = smem_addr(smem);
-    const uint32_t q_s = smem0;
+    const uint32_t q_s = smem0 + (uint32_t)li * 16u;             // this lane's slice of row 0
     const uint32_t do_s = q_s + (uint32_t)p.QB * ROWB;
-    const uint32_t sc_s = do_s + (uint32_t)p.QB * ROWB;
+    const uint32_t sc_s = smem0 + 2u * (uint32_t)p.QB * ROWB;
     const uint32_t bar = sc_s + (((uint32_t)p.QB * p.S * 8u + 15u) & ~15u);
 
     if (threadIdx.x == 0) {
@@ -221,8 +242,8 @@ __global__ void __launch_bounds__(512, 1) bwd_gather_kernel(const GatherParams p
             const unsigned rows_b = (unsigned)len * ROWB, sc_b = ((unsigned)len * p.S * 8u + 15u) & ~15u;
             fence_proxy_async();
             mbar_expect_tx(bar, 2u * rows_b + sc_b);
-            bulk_g2s_chunked(q_s, (const char*)p.q + qrow0 * ROWB, rows_b, bar);
-            bulk_g2s_chunked(do_s, (const char*)p.dout + qrow0 * ROWB, rows_b, bar);
+            bulk_g2s_chunked(smem0, (const char*)p.q + qrow0 * ROWB, rows_b, bar);
+            bulk_g2s_chunked(smem0 + (uint32_t)p.QB * ROWB, (const char*)p.dout + qrow0 * ROWB, rows_b, bar);
             bulk_g2s_chunked(sc_s, (const char*)sc, sc_b, bar);
         }
         bool ok = mbar_wait_bounded(bar, (unsigned)t & 1u, p.err);
@@ -231,59 +252,93 @@ __global__ void __launch_bounds__(512, 1) bwd_gather_kernel(const GatherParams p
         if (ok) {
             const size_t seg = ((size_t)b * NT + t) * p.V + vk;
             const int* rowptr = p.rowptr + seg * (p.L + 1);
-            const uint2* entries = p.entries + seg * ((size_t)p.QB * p.S * 4);
-            for (int pix = gid; pix < p.L; pix += ngroups) {
-                const int beg = __ldg(rowptr + pix), end = __ldg(rowptr + pix + 1);
-                if (beg == end) continue;
-                float ak[EPL], av[EPL];
+            const uint4* entries4 = reinterpret_cast<const uint4*>(p.entries + seg * (size_t)p.seg_entries);
+            // Key pixels are dealt round-robin to the groups: neighbouring pixels have lists of
+            // similar length (also when the coordinates cluster), so the groups stay balanced.
+            // The walk is software-pipelined: the row pointers of the pixel after next and the
+            // first entries of the next pixel are requested before the current pixel's entries
+            // are processed, so that their L2 latency hides behind that work.
+            int pix = gid;
+            int beg = 0, end = 0, nbeg = 0, nend = 0;
+            if (pix < p.L) { beg = __ldg(rowptr + pix); end = __ldg(rowptr + pix + 1); }
+            if (pix + ngroups < p.L) { nbeg = __ldg(rowptr + pix + ngroups); nend = __ldg(rowptr + pix + ngroups + 1); }
+            uint4 first0 = make_uint4(0, 0, 0, 0), first1 = first0;
+            if (end > beg) { first0 = __ldg(entries4 + (beg >> 1)); first1 = __ldg(entries4 + (beg >> 1) + 1); }
+            while (pix < p.L) {
+                int n2beg = 0, n2end = 0;
+                if (pix + 2 * ngroups < p.L) {
+                    n2beg = __ldg(rowptr + pix + 2 * ngroups);
+                    n2end = __ldg(rowptr + pix + 2 * ngroups + 1);
+                }
+                uint4 nfirst0 = make_uint4(0, 0, 0, 0), nfirst1 = nfirst0;
+                if (nend > nbeg) { nfirst0 = __ldg(entries4 + (nbeg >> 1)); nfirst1 = __ldg(entries4 + (nbeg >> 1) + 1); }
+                if (end > beg) {
+                    // this CTA alone owns the (batch, head, key view) maps, so the update is a plain
+                    // read-modify-write; the read is issued now and hides behind the entry loop
+                    float4 gk[CH * (EPV / 4)], gv[CH * (EPV / 4)];
 #pragma unroll
-                for (int e = 0; e < EPL; ++e) ak[e] = av[e] = 0.0f;
-                for (int e0 = beg; e0 < end; e0 += 4) {
-                    // four entries in flight; a clamped repeat of the last one gets weight 0
-                    uint2 ent[4];
+                    for (int ch = 0; ch < CH; ++ch)
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) ent[u] = __ldg(entries + min(e0 + u, end - 1));
+                        for (int k = 0; k < EPV / 4; ++k) {
+                            const size_t off = (size_t)pix * D + (size_t)(ch * G + li) * EPV + 4 * k;
+                            gk[ch * (EPV / 4) + k] = *reinterpret_cast<const float4*>(dkmap + off);
+                            gv[ch * (EPV / 4) + k] = *reinterpret_cast<const float4*>(dvmap + off);
+                        }
+                    float2 ak[HP], av[HP];
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const uint32_t ql = ent[u].x & 0xffffu, s = ent[u].x >> 16;
-                        const float w = e0 + u < end ? __uint_as_float(ent[u].y) : 0.0f;
-                        float2 sc;
-                        asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];"
-                                     : "=f"(sc.x), "=f"(sc.y) : "r"(sc_s + (ql * (uint32_t)p.S + s) * 8u));
-                        const float aw = sc.x * w, pw = sc.y * w;
+                    for (int e = 0; e < HP; ++e) ak[e] = av[e] = make_float2(0.0f, 0.0f);
+                    // four entries (32 bytes) per step, the next four already in flight; lists are
+                    // padded to a multiple of four with zero-weight entries
+                    uint4 nx0 = first0, nx1 = first1;
+                    for (int e0 = beg; e0 < end; e0 += 4) {
+                        const uint4 c0 = nx0, c1 = nx1;
+                        if (e0 + 4 < end) {
+                            nx0 = __ldg(entries4 + ((e0 + 4) >> 1));
+                            nx1 = __ldg(entries4 + ((e0 + 4) >> 1) + 1);
+                        }
+                        const uint32_t tags[4] = { c0.x, c0.z, c1.x, c1.z };
+                        const float ws[4] = { __uint_as_float(c0.y), __uint_as_float(c0.w), __uint_as_float(c1.y),
+                                              __uint_as_float(c1.w) };
 #pragma unroll
-                        for (int ch = 0; ch < CH; ++ch) {
-                            float fq[EPV], fd[EPV];
-                            unpack16(lds128(q_s + ql * ROWB + (uint32_t)(ch * G + li) * 16u), fq, (T*)nullptr);
-                            unpack16(lds128(do_s + ql * ROWB + (uint32_t)(ch * G + li) * 16u), fd, (T*)nullptr);
+                        for (int u = 0; u < 4; ++u) {
+                            const uint32_t roff = (tags[u] & 0xffffu) << 4, soff = (tags[u] >> 16) << 3;
+                            float2 sc;
+                            asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(sc.x), "=f"(sc.y) : "r"(sc_s + soff));
+                            const float aw = sc.x * ws[u], pw = sc.y * ws[u];
+                            const float2 aw2 = make_float2(aw, aw), pw2 = make_float2(pw, pw);
 #pragma unroll
-                            for (int k = 0; k < EPV; ++k) {
-                                ak[ch * EPV + k] = fmaf(aw, fq[k], ak[ch * EPV + k]);
-                                av[ch * EPV + k] = fmaf(pw, fd[k], av[ch * EPV + k]);
+                            for (int ch = 0; ch < CH; ++ch) {
+                                float2 fq[HV], fd[HV];
+                                unpack16_pairs(lds128(q_s + roff + (uint32_t)(ch * G) * 16u), fq, (T*)nullptr);
+                                unpack16_pairs(lds128(do_s + roff + (uint32_t)(ch * G) * 16u), fd, (T*)nullptr);
+#pragma unroll
+                                for (int k = 0; k < HV; ++k) {
+                                    ak[ch * HV + k] = __ffma2_rn(aw2, fq[k], ak[ch * HV + k]);
+                                    av[ch * HV + k] = __ffma2_rn(pw2, fd[k], av[ch * HV + k]);
+                                }
                             }
                         }
                     }
+#pragma unroll
+                    for (int ch = 0; ch < CH; ++ch)
+#pragma unroll
+                        for (int k = 0; k < EPV / 4; ++k) {
+                            const size_t off = (size_t)pix * D + (size_t)(ch * G + li) * EPV + 4 * k;
+                            float4 a = gk[ch * (EPV / 4) + k], c = gv[ch * (EPV / 4) + k];
+                            const int e = ch * HV + 2 * k;
+                            a.x += ak[e].x; a.y += ak[e].y; a.z += ak[e + 1].x; a.w += ak[e + 1].y;
+                            c.x += av[e].x; c.y += av[e].y; c.z += av[e + 1].x; c.w += av[e + 1].y;
+                            *reinterpret_cast<float4*>(dkmap + off) = a;
+                            *reinterpret_cast<float4*>(dvmap + off) = c;
+                        }
                 }
-                // this CTA alone owns the (batch, head, key view) maps: plain read-modify-write
-#pragma unroll
-                for (int ch = 0; ch < CH; ++ch)
-#pragma unroll
-                    for (int k = 0; k < EPV; k += 4) {
-                        const size_t off = (size_t)pix * D + (size_t)(ch * G + li) * EPV + k;
-                        float4* pk = reinterpret_cast<float4*>(dkmap + off);
-                        float4* pv = reinterpret_cast<float4*>(dvmap + off);
-                        float4 a = *pk, c = *pv;
-                        a.x += ak[ch * EPV + k]; a.y += ak[ch * EPV + k + 1];
-                        a.z += ak[ch * EPV + k + 2]; a.w += ak[ch * EPV + k + 3];
-                        c.x += av[ch * EPV + k]; c.y += av[ch * EPV + k + 1];
-                        c.z += av[ch * EPV + k + 2]; c.w += av[ch * EPV + k + 3];
-                        *pk = a;
-                        *pv = c;
-                    }
+                pix += ngroups;
+                beg = nbeg; end = nend;
+                nbeg = n2beg; nend = n2end;
+                first0 = nfirst0; first1 = nfirst1;
             }
         }
-        // every group is done with the tile (and its global updates are ordered before the
-        // next tile's by the barrier) before the buffers are refilled
+        // every group is done with the tile before its buffers are refilled
         if (__syncthreads_or(ok ? 0 : 1)) return;
     }
 }

@@ -62,6 +62,23 @@ __device__ __forceinline__ void unpack16(const uint4& r, float (&f)[8], __half*)
     }
 }
 
+// The same, as fp32 PAIRS (operands of fma.rn.f32x2): element 2i in .x, 2i+1 in .y.
+__device__ __forceinline__ void unpack16_pairs(const uint4& r, float2 (&f)[2], float*) {
+    f[0] = make_float2(__uint_as_float(r.x), __uint_as_float(r.y));
+    f[1] = make_float2(__uint_as_float(r.z), __uint_as_float(r.w));
+}
+__device__ __forceinline__ void unpack16_pairs(const uint4& r, float2 (&f)[4], __nv_bfloat16*) {
+    const uint32_t w[4] = { r.x, r.y, r.z, r.w };
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        f[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+}
+__device__ __forceinline__ void unpack16_pairs(const uint4& r, float2 (&f)[4], __half*) {
+    const uint32_t w[4] = { r.x, r.y, r.z, r.w };
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+}
+
 __device__ __forceinline__ uint4 pack16(const float (&f)[4], float*) {
     return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
 }

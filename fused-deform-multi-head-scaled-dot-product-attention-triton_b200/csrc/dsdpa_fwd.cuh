@@ -15,6 +15,9 @@
 // into shared memory with 1-D bulk copies (cp.async.bulk, completion on an mbarrier),
 // double-buffered when two views fit.  Otherwise rows are gathered from L2/L1 with
 // ld.global.nc.
+//
+// Arithmetic is fp32 throughout, two lanes at a time (fma.rn.f32x2) where the data
+// comes in pairs.
 #pragma once
 
 #include "dsdpa_common.cuh"
@@ -39,8 +42,17 @@ struct FwdParams {
 };
 
 // Per-warp scratch that hands the decoded corners of 32 samples from the lane that
-// decoded them to the group that consumes them.
+// decoded them to the group that consumes them: 32 weight records, then 32 pixel records.
 constexpr int kRecBytesPerWarp = 32 * 16 * 2;
+
+// Slot of the record of sample i (0..G-1) of group g inside the per-warp scratch.
+// The NG records one step reads are contiguous (conflict-free broadcast reads), and
+// the rotation by i/2 spreads the G records a group writes at once over all banks.
+template <int G, int NG>
+__device__ __forceinline__ uint32_t rec_slot(int i, int g) {
+    if constexpr (NG == 4) return (uint32_t)(i * NG + ((g + (i >> 1)) & 3));
+    else return (uint32_t)(i * NG + g);
+}
 
 template <typename T, int D, bool STAGED>
 struct MapReader {
@@ -57,11 +69,12 @@ struct MapReader {
     }
 };
 
-// k~ or v~ slice of this lane: sum over the four corners of w_c * row_c.
+// k~ or v~ slice of this lane: sum over the four corners of w_c * row_c, as EPL/2 pairs.
 template <typename T, int D, bool STAGED>
 __device__ __forceinline__ void gather_interp(const MapReader<T, D, STAGED>& map, const int (&pix)[4],
-                                              const float (&w)[4], int li, float (&dst)[RowCfg<T, D>::EPL]) {
+                                              const float2 (&w2)[4], int li, float2 (&dst)[RowCfg<T, D>::EPL / 2]) {
     using RC = RowCfg<T, D>;
+    constexpr int HV = RC::EPV / 2;  // pairs per 16-byte vector
     uint4 raw[4][RC::CH];
 #pragma unroll
     for (int c = 0; c < 4; ++c)
@@ -69,19 +82,39 @@ __device__ __forceinline__ void gather_interp(const MapReader<T, D, STAGED>& map
         for (int ch = 0; ch < RC::CH; ++ch) raw[c][ch] = map.load(pix[c], ch * RC::G + li);
 #pragma unroll
     for (int ch = 0; ch < RC::CH; ++ch) {
-        float f[4][RC::EPV];
+        float2 f[4][HV];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) unpack16(raw[c][ch], f[c], (T*)nullptr);
+        for (int c = 0; c < 4; ++c) unpack16_pairs(raw[c][ch], f[c], (T*)nullptr);
 #pragma unroll
-        for (int e = 0; e < RC::EPV; ++e)
-            dst[ch * RC::EPV + e] = fmaf(w[0], f[0][e], fmaf(w[1], f[1][e], fmaf(w[2], f[2][e], w[3] * f[3][e])));
+        for (int e = 0; e < HV; ++e) {
+            float2 a = __fmul2_rn(w2[3], f[3][e]);
+            a = __ffma2_rn(w2[2], f[2][e], a);
+            a = __ffma2_rn(w2[1], f[1][e], a);
+            dst[ch * HV + e] = __ffma2_rn(w2[0], f[0][e], a);
+        }
     }
+}
+
+// Decode the sample of this lane and publish its record for the step that consumes it.
+template <int G, int NG>
+__device__ __forceinline__ void publish_record(const float2* cptr, int s, int S, int W, int H, float hw, float hh,
+                                               uint32_t rec_w, uint32_t rec_p, int li, int g) {
+    float2 c = make_float2(0.0f, 0.0f);
+    if (s < S) c = __ldg(cptr + s);
+    Corners cr;
+    float fx, fy;
+    decode_corners(c.x, c.y, W, H, hw, hh, cr, fx, fy);
+    const uint32_t r = rec_slot<G, NG>(li, g) * 16u;
+    sts128(rec_w + r, make_uint4(__float_as_uint(cr.w[0]), __float_as_uint(cr.w[1]), __float_as_uint(cr.w[2]),
+                                 __float_as_uint(cr.w[3])));
+    sts128(rec_p + r, make_uint4((uint32_t)cr.pix[0], (uint32_t)cr.pix[1], (uint32_t)cr.pix[2], (uint32_t)cr.pix[3]));
 }
 
 template <typename T, int D, int NQ, bool STAGED, int MAXT, int MINB>
 __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
     using RC = RowCfg<T, D>;
     constexpr int G = RC::G, NG = RC::NG, EPL = RC::EPL, CH = RC::CH, EPV = RC::EPV, ROWB = RC::ROWB;
+    constexpr int HP = EPL / 2;  // fp32 pairs per lane
     extern __shared__ __align__(128) unsigned char smem[];
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -118,13 +151,14 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
         }
     }
 
-    float m_run[NQ], l_run[NQ], acc[NQ][EPL];
+    float m_run[NQ], l_run[NQ];
+    float2 acc[NQ][HP];
 #pragma unroll
     for (int j = 0; j < NQ; ++j) {
         m_run[j] = -INFINITY;
         l_run[j] = 0.0f;
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) acc[j][e] = 0.0f;
+        for (int e = 0; e < HP; ++e) acc[j][e] = make_float2(0.0f, 0.0f);
     }
 
     for (int vk = 0; vk < p.V; ++vk) {
@@ -161,55 +195,52 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
                 const int qi = min(qslot, qend - 1);  // surplus groups redo the last query; never stored
                 const int vq = qi / p.L, l = qi - vq * p.L;
                 const size_t qrow = (((size_t)b * p.V + vq) * p.Hh + h) * p.L + l;
-                float qf[EPL];
+                float2 qf[HP];
 #pragma unroll
                 for (int ch = 0; ch < CH; ++ch) {
-                    uint4 raw = ldg128_nc((const char*)p.q + qrow * ROWB + (size_t)(ch * G + li) * 16);
-                    float f[EPV];
-                    unpack16(raw, f, (T*)nullptr);
+                    float2 f[EPV / 2];
+                    unpack16_pairs(ldg128_nc((const char*)p.q + qrow * ROWB + (size_t)(ch * G + li) * 16), f, (T*)nullptr);
 #pragma unroll
-                    for (int e = 0; e < EPV; ++e) qf[ch * EPV + e] = f[e] * p.scale2;
+                    for (int e = 0; e < EPV / 2; ++e)
+                        qf[ch * (EPV / 2) + e] = make_float2(f[e].x * p.scale2, f[e].y * p.scale2);
                 }
                 const float2* cptr = reinterpret_cast<const float2*>(p.coords) +
                                      ((((size_t)b * p.V + vq) * p.L + l) * p.V + vk) * (size_t)p.S;
                 float m = m_run[j], lsum = l_run[j];
                 for (int s0 = 0; s0 < p.S; s0 += G) {
-                    {
-                        const int s = s0 + li;
-                        float2 c = make_float2(0.0f, 0.0f);
-                        if (s < p.S) c = __ldg(cptr + s);
-                        Corners cr;
-                        float fx, fy;
-                        decode_corners(c.x, c.y, p.W, p.H, p.hw, p.hh, cr, fx, fy);
-                        const uint32_t r = (uint32_t)(li * NG + g) * 16u;
-                        sts128(rec_w + r, make_uint4(__float_as_uint(cr.w[0]), __float_as_uint(cr.w[1]),
-                                                     __float_as_uint(cr.w[2]), __float_as_uint(cr.w[3])));
-                        sts128(rec_p + r, make_uint4((uint32_t)cr.pix[0], (uint32_t)cr.pix[1],
-                                                     (uint32_t)cr.pix[2], (uint32_t)cr.pix[3]));
-                    }
+                    publish_record<G, NG>(cptr, s0 + li, p.S, p.W, p.H, p.hw, p.hh, rec_w, rec_p, li, g);
                     __syncwarp();
                     const int cnt = min(G, p.S - s0);
 #pragma unroll 2
                     for (int i = 0; i < cnt; ++i) {
-                        const uint32_t r = (uint32_t)(i * NG + g) * 16u;
+                        const uint32_t r = rec_slot<G, NG>(i, g) * 16u;
                         const uint4 wr = lds128(rec_w + r), pr = lds128(rec_p + r);
-                        const float w[4] = { __uint_as_float(wr.x), __uint_as_float(wr.y),
-                                             __uint_as_float(wr.z), __uint_as_float(wr.w) };
+                        const float w0 = __uint_as_float(wr.x), w1 = __uint_as_float(wr.y);
+                        const float w2_ = __uint_as_float(wr.z), w3 = __uint_as_float(wr.w);
+                        const float2 w2[4] = { make_float2(w0, w0), make_float2(w1, w1), make_float2(w2_, w2_),
+                                               make_float2(w3, w3) };
                         const int pix[4] = { (int)pr.x, (int)pr.y, (int)pr.z, (int)pr.w };
-                        float kt[EPL], vt[EPL];
-                        gather_interp<T, D, STAGED>(kmap, pix, w, li, kt);
-                        gather_interp<T, D, STAGED>(vmap, pix, w, li, vt);
-                        float part = 0.0f;
+                        float2 kt[HP], vt[HP];
+                        gather_interp<T, D, STAGED>(kmap, pix, w2, li, kt);
+                        gather_interp<T, D, STAGED>(vmap, pix, w2, li, vt);
+                        float2 part = __fmul2_rn(qf[0], kt[0]);
 #pragma unroll
-                        for (int e = 0; e < EPL; ++e) part = fmaf(qf[e], kt[e], part);
-                        const float sc = group_sum<G>(part);
-                        const float m_new = fmaxf(m, sc);
-                        const float alpha = fast_exp2(m - m_new);
-                        const float pe = fast_exp2(sc - m_new);
-                        lsum = fmaf(lsum, alpha, pe);
+                        for (int e = 1; e < HP; ++e) part = __ffma2_rn(qf[e], kt[e], part);
+                        const float sc = group_sum<G>(part.x + part.y);
+                        if (sc > m) {
+                            // new running maximum: rescale what has been accumulated so far
+                            const float alpha = fast_exp2(m - sc);
+                            lsum *= alpha;
+                            const float2 a2 = make_float2(alpha, alpha);
 #pragma unroll
-                        for (int e = 0; e < EPL; ++e) acc[j][e] = fmaf(pe, vt[e], acc[j][e] * alpha);
-                        m = m_new;
+                            for (int e = 0; e < HP; ++e) acc[j][e] = __fmul2_rn(acc[j][e], a2);
+                            m = sc;
+                        }
+                        const float pe = fast_exp2(sc - m);
+                        lsum += pe;
+                        const float2 p2 = make_float2(pe, pe);
+#pragma unroll
+                        for (int e = 0; e < HP; ++e) acc[j][e] = __ffma2_rn(p2, vt[e], acc[j][e]);
                     }
                     __syncwarp();
                 }
@@ -240,7 +271,10 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
         for (int ch = 0; ch < CH; ++ch) {
             float f[EPV];
 #pragma unroll
-            for (int e = 0; e < EPV; ++e) f[e] = acc[j][ch * EPV + e] * inv;
+            for (int e = 0; e < EPV / 2; ++e) {
+                f[2 * e] = acc[j][ch * (EPV / 2) + e].x * inv;
+                f[2 * e + 1] = acc[j][ch * (EPV / 2) + e].y * inv;
+            }
             stg128((char*)p.out + qrow * ROWB + (size_t)(ch * G + li) * 16, pack16(f, (T*)nullptr));
         }
         if (li == 0) p.lse[qrow] = m_run[j] + log2f(l_run[j]);

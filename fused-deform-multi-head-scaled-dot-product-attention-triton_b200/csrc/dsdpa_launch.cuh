@@ -40,9 +40,10 @@ inline cudaError_t allow_big_smem(K kern, bool (&done)[64]) {
     return e;
 }
 
-template <typename T, int D, int NQ, bool STAGED>
+template <typename T, int D, int NQ, bool STAGED, int MAXT = (STAGED ? kStagedMaxThreads : kL2MaxThreads)>
 inline cudaError_t fwd_one(const FwdParams& p, const TilePlan& plan, cudaStream_t stream) {
-    auto kern = fwd_kernel<T, D, NQ, STAGED, STAGED ? kStagedMaxThreads : kL2MaxThreads, STAGED ? 1 : 2>;
+    auto kern = fwd_kernel<T, D, NQ, STAGED, MAXT, STAGED ? 1 : 2>;
+    if (plan.nw * 32 > MAXT) return cudaErrorInvalidValue;
     static bool done[64] = {};  // a benign race at worst repeats the attribute call
     cudaError_t e = allow_big_smem(kern, done);
     if (e != cudaSuccess) return e;

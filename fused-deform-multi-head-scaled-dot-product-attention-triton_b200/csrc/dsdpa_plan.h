@@ -49,6 +49,7 @@ struct GatherPlan {
     size_t gather_smem;
     long long gather_ctas;   // B*Hh*V
     long long segments;      // B * (V*tpv) * V index segments
+    int seg_entries;         // index entries reserved per segment
     size_t index_smem;
     // byte offsets inside the workspace (after the fp32 dK/dV accumulators, if any)
     size_t scal_bytes, entries_bytes, rowptr_bytes;
