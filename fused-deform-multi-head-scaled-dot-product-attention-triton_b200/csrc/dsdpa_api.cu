@@ -90,7 +90,10 @@ TilePlan plan_tiles(const dsdpa_problem& p, bool backward, bool allow_priv) {
                 const long long waves = (ctas + kPlanSMs - 1) / kPlanSMs;
                 // one warp step moves 8*CH 128-bit loads = 32*CH shared-memory wavefronts
                 const double wf = 32.0 * ch * (backward ? 2.5 : 1.0);
-                const double step = nw * wf > 400.0 ? nw * wf : 400.0;
+                // a warp's step takes about a thousand cycles end to end (measured), so a CTA is
+                // latency-bound until it has enough warps to cover that with wavefronts
+                const double lat = backward ? 1200.0 : 1000.0;
+                const double step = nw * wf > lat ? nw * wf : lat;
                 const double stage_cost = nstage == 1 ? 2.0 * (double)map_bytes / 48.0 : 0.0;
                 const double flush_cost = want_priv ? 2.0 * (double)acc_bytes / 32.0 : 0.0;
                 const double cta_time = p.V * ((double)rounds * p.S * step + stage_cost + flush_cost + 2000.0);
