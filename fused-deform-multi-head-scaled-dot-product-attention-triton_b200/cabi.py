@@ -33,11 +33,15 @@ FLAG_DETERMINISTIC = 0x2
 FLAG_SCATTER_GLOBAL = 0x4
 FLAG_SCATTER = 0x8
 
+# limit of dsdpa_backward_static_scratch (DSDPA_STATIC_SCRATCH_BYTES)
+STATIC_SCRATCH_BYTES = 64 << 20
+
 # Every symbol include/dsdpa.h declares (checked by the CPU test-suite).
 EXPORTS = (
     "dsdpa_forward",
     "dsdpa_backward_workspace_bytes",
     "dsdpa_backward",
+    "dsdpa_backward_static_scratch",
     "dsdpa_status_string",
     "dsdpa_version",
     "dsdpa_last_cuda_error",
@@ -85,6 +89,8 @@ def lib() -> ctypes.CDLL:
     L.dsdpa_backward_workspace_bytes.restype = ctypes.c_size_t
     L.dsdpa_backward.argtypes = [pp] + [vp] * 11 + [vp, ctypes.c_size_t, ci, vp]
     L.dsdpa_backward.restype = ci
+    L.dsdpa_backward_static_scratch.argtypes = [pp] + [vp] * 10 + [ci, vp]
+    L.dsdpa_backward_static_scratch.restype = ci
     L.dsdpa_status_string.argtypes = [ci]
     L.dsdpa_status_string.restype = ctypes.c_char_p
     L.dsdpa_version.argtypes = []

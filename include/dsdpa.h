@@ -102,6 +102,34 @@ int dsdpa_backward(const dsdpa_problem* p,
                    void* dq, void* dk, void* dv, float* dcoords,
                    void* workspace, size_t workspace_bytes, int device, void* stream);
 
+/*
+ * Backward without caller-provided scratch.  (No counterpart in the reference: its backward
+ * allocates its accumulators with torch on every call, ops/triton.py:427-430, which is
+ * exactly what the callers of this entry point are not allowed to do.)
+ *
+ * For callers that cannot allocate device memory at the point where the backward runs --
+ * a serving loop with a frozen memory budget, a plugin inside a host that owns the device
+ * heap, a callback running under the allocator's lock -- the scratch dsdpa_backward asks
+ * its caller for is taken from a fixed array that is part of the library image:
+ * DSDPA_STATIC_SCRATCH_BYTES of device memory on every GPU that loads the library, from
+ * load until process exit.  The call allocates and frees nothing (no cudaMalloc/cudaFree,
+ * no allocating library routine); inputs and outputs are still the caller's.
+ *
+ *   - Same results, arguments and flags as dsdpa_backward with dcoords == NULL.
+ *   - A problem whose dsdpa_backward_workspace_bytes exceeds DSDPA_STATIC_SCRATCH_BYTES is
+ *     refused with DSDPA_ERR_TOO_LARGE before any work is enqueued.
+ *   - The first call on a device looks up the array's device address (a symbol lookup, not
+ *     an allocation).  Make that first call outside any stream capture.
+ *   - All calls on a device share the one array, which keeps the previous call's contents;
+ *     what has to start at zero is cleared on `stream` by every call.  Calls whose GPU work
+ *     overlaps (other streams, other host threads) race on it: keep them on one stream.
+ */
+#define DSDPA_STATIC_SCRATCH_BYTES (64u << 20)
+int dsdpa_backward_static_scratch(const dsdpa_problem* p,
+                                  const void* q, const void* k, const void* v, const float* coords,
+                                  const void* out, const float* lse, const void* dout,
+                                  void* dq, void* dk, void* dv, int device, void* stream);
+
 /* Human-readable name of a dsdpa_status. */
 const char* dsdpa_status_string(int status);
 
