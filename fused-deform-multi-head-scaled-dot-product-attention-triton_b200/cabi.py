@@ -50,6 +50,7 @@ EXPORTS = (
     "dsdpa_describe_plan",
     "dsdpa_probe_l2_read_bandwidth",
     "dsdpa_probe_shared_read_bandwidth",
+    "dsdpa_probe_shared_row_gather_bandwidth",
 )
 
 
@@ -107,6 +108,8 @@ def lib() -> ctypes.CDLL:
     L.dsdpa_probe_l2_read_bandwidth.restype = ci
     L.dsdpa_probe_shared_read_bandwidth.argtypes = [ci, ci, vp, ctypes.POINTER(ctypes.c_double)]
     L.dsdpa_probe_shared_read_bandwidth.restype = ci
+    L.dsdpa_probe_shared_row_gather_bandwidth.argtypes = [ci, ci, vp, ctypes.POINTER(ctypes.c_double)]
+    L.dsdpa_probe_shared_row_gather_bandwidth.restype = ci
     _lib = L
     return L
 

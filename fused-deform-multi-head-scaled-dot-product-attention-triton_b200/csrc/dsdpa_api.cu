@@ -240,6 +240,29 @@ __global__ void __launch_bounds__(1024, 1) probe_smem_kernel(int rounds) {
     if (acc == 0x9e3779b9u) g_probe_sink = acc;
 }
 
+// The access pattern of the kernels' gathers: every group of eight lanes reads one 128-byte
+// row at a pseudo-random row index of a 64 KB window (row-aligned, so each group is
+// conflict-free by itself; different groups of a warp hit unrelated rows).
+__global__ void __launch_bounds__(1024, 1) probe_smem_rows_kernel(int rounds) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const uint32_t base = smem_addr(smem);
+    for (uint32_t o = threadIdx.x * 16u; o < 65536u; o += blockDim.x * 16u) sts128(base + o, make_uint4(o, o + 1, o + 2, o + 3));
+    __syncthreads();
+    unsigned acc = 0;
+    const uint32_t li = threadIdx.x & 7u;
+    uint32_t state = (threadIdx.x >> 3) * 2654435761u + 12345u;   // one generator per group
+    for (int r = 0; r < rounds; ++r) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            state = state * 1664525u + 1013904223u;
+            const uint32_t row = (state >> 13) & 511u;             // 512 rows of 128 bytes
+            const uint4 x = lds128(base + row * 128u + li * 16u);
+            acc ^= x.x ^ x.y ^ x.z ^ x.w;
+        }
+    }
+    if (acc == 0x9e3779b9u) g_probe_sink = acc;
+}
+
 }  // namespace dsdpa
 
 using namespace dsdpa;
@@ -492,6 +515,23 @@ int dsdpa_probe_l2_read_bandwidth(const void* buffer, size_t bytes, int iters, i
     if (guard.err != cudaSuccess) return cuda_fail(guard.err);
     L2Ctx c{ (const uint4*)buffer, bytes / 16 / 4096 * 4096, kSMs };
     return time_probe((cudaStream_t)stream, iters, (double)c.nvec * 16.0 * c.ctas, gbps, launch_l2, &c);
+}
+
+static void launch_smem_rows(cudaStream_t s, void* c) {
+    SmemCtx* x = (SmemCtx*)c;
+    probe_smem_rows_kernel<<<x->ctas, 1024, 65536, s>>>(x->rounds);
+}
+
+int dsdpa_probe_shared_row_gather_bandwidth(int iters, int device, void* stream, double* gbps) {
+    if (!gbps) return DSDPA_ERR_NULL_POINTER;
+    if (iters <= 0) return DSDPA_ERR_BAD_SHAPE;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return cuda_fail(guard.err);
+    cudaError_t e = cudaFuncSetAttribute(probe_smem_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
+    if (e != cudaSuccess) return cuda_fail(e);
+    SmemCtx c{ 4096, kSMs };
+    return time_probe((cudaStream_t)stream, iters, (double)c.rounds * 8.0 * 16.0 * 1024.0 * c.ctas, gbps, launch_smem_rows,
+                      &c);
 }
 
 int dsdpa_probe_shared_read_bandwidth(int iters, int device, void* stream, double* gbps) {
