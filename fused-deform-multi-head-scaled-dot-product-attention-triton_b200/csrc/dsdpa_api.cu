@@ -368,7 +368,6 @@ int dsdpa_backward(const dsdpa_problem* p, const void* q, const void* k, const v
         misaligned(dout) || misaligned(dq) || misaligned(dk) || misaligned(dv) || misaligned(workspace) ||
         misaligned(dcoords))
         return DSDPA_ERR_MISALIGNED;
-    if (dcoords) return DSDPA_ERR_BAD_FLAGS;  // coordinate gradient: not in this build
     const size_t need = dsdpa_backward_workspace_bytes(p);
     if (need > 0 && (!workspace || workspace_bytes < need)) return DSDPA_ERR_WORKSPACE;
     DeviceGuard guard(device);
@@ -380,7 +379,13 @@ int dsdpa_backward(const dsdpa_problem* p, const void* q, const void* k, const v
 
     const GatherPlan gp = plan_gather(*p);
     const bool two_pass = use_two_pass(*p, gp);
+    // the coordinate gradient is computed by the two-pass form's first pass only
+    if (dcoords && !two_pass) return DSDPA_ERR_BAD_FLAGS;
     const size_t n = (size_t)p->B * p->V * p->Hh * p->W * p->H * p->D;
+    if (dcoords) {
+        const size_t nc = (size_t)p->B * p->V * p->W * p->H * p->V * p->S * 2;
+        if ((e = cudaMemsetAsync(dcoords, 0, nc * sizeof(float), s)) != cudaSuccess) return cuda_fail(e);
+    }
     const size_t acc_bytes = p->dtype == DSDPA_F32 ? 0 : ((2 * n * sizeof(float) + 255) & ~(size_t)255);
     float* dk32 = p->dtype == DSDPA_F32 ? (float*)dk : (float*)workspace;
     float* dv32 = p->dtype == DSDPA_F32 ? (float*)dv : (float*)workspace + n;
@@ -427,9 +432,9 @@ int dsdpa_backward(const dsdpa_problem* p, const void* q, const void* k, const v
     bp.tpv = gp.tpv;
     bp.QB = gp.QB;
     switch (p->dtype) {
-        case DSDPA_F32: e = launch_backward_main<float>(bp, plan, p->D, two_pass, s); break;
-        case DSDPA_BF16: e = launch_backward_main<__nv_bfloat16>(bp, plan, p->D, two_pass, s); break;
-        default: e = launch_backward_main<__half>(bp, plan, p->D, two_pass, s); break;
+        case DSDPA_F32: e = launch_backward_main<float>(bp, plan, p->D, two_pass, dcoords != nullptr, s); break;
+        case DSDPA_BF16: e = launch_backward_main<__nv_bfloat16>(bp, plan, p->D, two_pass, dcoords != nullptr, s); break;
+        default: e = launch_backward_main<__half>(bp, plan, p->D, two_pass, dcoords != nullptr, s); break;
     }
     if (e != cudaSuccess) return cuda_fail(e);
     g_launches += 1;

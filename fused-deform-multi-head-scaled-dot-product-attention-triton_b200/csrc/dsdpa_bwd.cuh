@@ -52,10 +52,16 @@ struct BwdParams {
 
 // TWOPASS: no scatter; instead every sample's (sm_scale*ds, p) is written out for the
 // gather pass (bwd_gather_kernel) that forms dK/dV without atomics.
-template <typename T, int D, int NQ, bool STAGED, bool PRIV, bool TWOPASS, int MAXT, int MINB>
+// DCOORDS (two-pass form only): additionally d(loss)/d(coords), summed over the heads with
+// red.global.add.v2.f32.  With k~ = sum_c w_c K_c and A_c = q.K_c, B_c = dout.V_c the gradient
+// w.r.t. the pixel position is  a*(d w_c/dx) A_c + p*(d w_c/dx) B_c  summed over the valid
+// corners (a = sm_scale*ds), times (W-1) resp. (H-1) for the normalised coordinate
+// (grid_sample backward w.r.t. the grid chained through grid = c*2-1, ops/torch.py:14).
+template <typename T, int D, int NQ, bool STAGED, bool PRIV, bool TWOPASS, bool DCOORDS, int MAXT, int MINB>
 __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams p) {
     static_assert(!PRIV || STAGED, "privatised accumulators live next to staged maps");
     static_assert(!(PRIV && TWOPASS), "the two-pass form has nothing to privatise");
+    static_assert(!DCOORDS || TWOPASS, "the coordinate gradient is built into the two-pass form only");
     using RC = RowCfg<T, D>;
     constexpr int G = RC::G, NG = RC::NG, EPL = RC::EPL, CH = RC::CH, EPV = RC::EPV, ROWB = RC::ROWB;
     constexpr int HP = EPL / 2, HV = EPV / 2;  // fp32 pairs per lane / per 16-byte vector
@@ -189,33 +195,82 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
                 }
                 for (int s0 = 0; s0 < p.S; s0 += G) {
                     float my_a = 0.0f, my_p = 0.0f;  // TWOPASS: scalars of sample s0+li
-                    publish_record<G, NG>(cptr, s0 + li, p.S, p.W, p.H, p.hw, p.hh, rec_w, rec_p, li, g);
+                    if constexpr (DCOORDS) {
+                        publish_record_dc<G, NG>(cptr, s0 + li, p.S, p.W, p.H, p.hw, p.hh, rec_w, rec_p, li, g);
+                    } else {
+                        publish_record<G, NG>(cptr, s0 + li, p.S, p.W, p.H, p.hw, p.hh, rec_w, rec_p, li, g);
+                    }
+                    float my_gx = 0.0f, my_gy = 0.0f;  // DCOORDS: gradient of sample s0+li
                     __syncwarp();
                     const int cnt = min(G, p.S - s0);
                     for (int i = 0; i < cnt; ++i) {
                         const uint32_t r = rec_slot<G, NG>(i, g) * 16u;
                         const uint4 wr = lds128(rec_w + r), pr = lds128(rec_p + r);
-                        const float w[4] = { __uint_as_float(wr.x), __uint_as_float(wr.y),
-                                             __uint_as_float(wr.z), __uint_as_float(wr.w) };
+                        float w[4];
+                        int pix[4] = { (int)pr.x, (int)pr.y, (int)pr.z, (int)pr.w };
+                        // DCOORDS: 1-D weights and the inside flags (see publish_record_dc)
+                        float wx0 = 0.0f, wx1 = 0.0f, wy0 = 0.0f, wy1 = 0.0f;
+                        uint32_t flags = 0;
+                        if constexpr (DCOORDS) {
+                            wx0 = __uint_as_float(wr.x); wx1 = __uint_as_float(wr.y);
+                            wy0 = __uint_as_float(wr.z); wy1 = __uint_as_float(wr.w);
+                            w[0] = wx0 * wy0; w[1] = wx1 * wy0; w[2] = wx0 * wy1; w[3] = wx1 * wy1;
+                            flags = pr.x >> 28;
+                            pix[0] = (int)(pr.x & kPixMask);
+                        } else {
+                            w[0] = __uint_as_float(wr.x); w[1] = __uint_as_float(wr.y);
+                            w[2] = __uint_as_float(wr.z); w[3] = __uint_as_float(wr.w);
+                        }
                         const float2 w2[4] = { make_float2(w[0], w[0]), make_float2(w[1], w[1]),
                                                make_float2(w[2], w[2]), make_float2(w[3], w[3]) };
-                        const int pix[4] = { (int)pr.x, (int)pr.y, (int)pr.z, (int)pr.w };
-                        float2 kt[HP], vt[HP];
-                        gather_interp<T, D, STAGED>(kmap, pix, w2, li, kt);
-                        gather_interp<T, D, STAGED>(vmap, pix, w2, li, vt);
-                        float2 ps = __fmul2_rn(qf[0], kt[0]), pd = __fmul2_rn(dof[0], vt[0]);
+                        float2 kt[HP];
+                        float sc, dp;        // logit in base-2 units, dout.v~
+                        float ax = 0.0f, ay = 0.0f, bx = 0.0f, by = 0.0f;  // DCOORDS: d/dx, d/dy of q.k~ and dout.v~
+                        if constexpr (!DCOORDS) {
+                            float2 vt[HP];
+                            gather_interp<T, D, STAGED>(kmap, pix, w2, li, kt);
+                            gather_interp<T, D, STAGED>(vmap, pix, w2, li, vt);
+                            float2 ps = __fmul2_rn(qf[0], kt[0]), pd = __fmul2_rn(dof[0], vt[0]);
 #pragma unroll
-                        for (int e = 1; e < HP; ++e) {
-                            ps = __ffma2_rn(qf[e], kt[e], ps);
-                            pd = __ffma2_rn(dof[e], vt[e], pd);
+                            for (int e = 1; e < HP; ++e) {
+                                ps = __ffma2_rn(qf[e], kt[e], ps);
+                                pd = __ffma2_rn(dof[e], vt[e], pd);
+                            }
+                            sc = group_sum<G>(ps.x + ps.y);
+                            dp = group_sum<G>(pd.x + pd.y);
+                        } else {
+                            // per-corner dots A_c = qf.K_c (qf carries scale2) and B_c = dout.V_c
+                            float2 ac[4], bc[4], unused[HP];
+                            corner_dots<T, D, STAGED, true>(kmap, pix, w2, li, qf, kt, ac);
+                            corner_dots<T, D, STAGED, false>(vmap, pix, w2, li, dof, unused, bc);
+                            float a4[4], b4[4];
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                a4[c] = group_sum<G>(ac[c].x + ac[c].y);
+                                b4[c] = group_sum<G>(bc[c].x + bc[c].y);
+                            }
+                            sc = w[0] * a4[0] + w[1] * a4[1] + w[2] * a4[2] + w[3] * a4[3];
+                            dp = w[0] * b4[0] + w[1] * b4[1] + w[2] * b4[2] + w[3] * b4[3];
+                            // a corner outside the map has value zero: drop its dot
+                            const float vx0 = (flags & 1u) ? 1.0f : 0.0f, vx1 = (flags & 2u) ? 1.0f : 0.0f;
+                            const float vy0 = (flags & 4u) ? 1.0f : 0.0f, vy1 = (flags & 8u) ? 1.0f : 0.0f;
+                            ax = wy0 * (vx1 * a4[1] - vx0 * a4[0]) + wy1 * (vx1 * a4[3] - vx0 * a4[2]);
+                            ay = wx0 * (vy1 * a4[2] - vy0 * a4[0]) + wx1 * (vy1 * a4[3] - vy0 * a4[1]);
+                            bx = wy0 * (vx1 * b4[1] - vx0 * b4[0]) + wy1 * (vx1 * b4[3] - vx0 * b4[2]);
+                            by = wx0 * (vy1 * b4[2] - vy0 * b4[0]) + wx1 * (vy1 * b4[3] - vy0 * b4[1]);
                         }
-                        const float sc = group_sum<G>(ps.x + ps.y);
-                        const float dp = group_sum<G>(pd.x + pd.y);
                         const float pe = fast_exp2(sc - lse);
                         const float ds = pe * (dp - delta);
                         const float2 ds2 = make_float2(ds, ds);
 #pragma unroll
                         for (int e = 0; e < HP; ++e) dq[j][e] = __ffma2_rn(ds2, kt[e], dq[j][e]);
+                        if constexpr (DCOORDS) {
+                            // sm_scale*ds*(q.dK_c/dx) = (ds*ln2)*ax because qf carries sm_scale*log2(e)
+                            if (i == li) {
+                                my_gx = ((ds * kLn2) * ax + pe * bx) * (float)(p.W - 1);
+                                my_gy = ((ds * kLn2) * ay + pe * by) * (float)(p.H - 1);
+                            }
+                        }
                         if constexpr (TWOPASS) {
                             if (i == li) {
                                 my_a = ds * p.sm_scale;
@@ -257,6 +312,13 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
                     if constexpr (TWOPASS) {
                         // one coalesced float2 per lane: the group writes G samples at once
                         if (live && li < cnt) scal_row[s0 + li] = make_float2(my_a, my_p);
+                    }
+                    if constexpr (DCOORDS) {
+                        // all heads add into the same coordinate gradient
+                        if (live && li < cnt) {
+                            float* dst = p.dcoords + (((((size_t)b * p.V + vq) * p.L + l) * p.V + vk) * (size_t)p.S + s0 + li) * 2;
+                            asm volatile("red.global.add.v2.f32 [%0], {%1,%2};" :: "l"(dst), "f"(my_gx), "f"(my_gy) : "memory");
+                        }
                     }
                     __syncwarp();
                 }

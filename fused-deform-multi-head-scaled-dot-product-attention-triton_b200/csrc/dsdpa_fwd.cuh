@@ -110,6 +110,74 @@ __device__ __forceinline__ void publish_record(const float2* cptr, int s, int S,
     sts128(rec_p + r, make_uint4((uint32_t)cr.pix[0], (uint32_t)cr.pix[1], (uint32_t)cr.pix[2], (uint32_t)cr.pix[3]));
 }
 
+// Record for the coordinate gradient.  The weight plane holds the ONE-dimensional weights
+// {wx0, wx1, wy0, wy1} = {1-fx, fx, 1-fy, fy}, each zeroed when its column / row lies outside the
+// map (the four corner weights are their products).  Whether a column / row is inside cannot
+// be read off a weight (fx may be exactly 0 for an inside column), so the four flags travel
+// in the top bits of the first pixel index: bit 28 column x0, 29 column x1, 30 row y0, 31 row y1.
+constexpr uint32_t kPixMask = 0x0fffffffu;
+
+template <int G, int NG>
+__device__ __forceinline__ void publish_record_dc(const float2* cptr, int s, int S, int W, int H, float hw, float hh,
+                                                  uint32_t rec_w, uint32_t rec_p, int li, int g) {
+    float2 c = make_float2(0.0f, 0.0f);
+    if (s < S) c = __ldg(cptr + s);
+    const float x = unnormalize(c.x, hw), y = unnormalize(c.y, hh);
+    const float xf = floorf(x), yf = floorf(y);
+    float fx = x - xf, fy = y - yf;
+    const bool xr = (xf >= -2.0f) && (xf <= (float)W + 1.0f), yr = (yf >= -2.0f) && (yf <= (float)H + 1.0f);
+    const int x0 = xr ? (int)xf : -2, y0 = yr ? (int)yf : -2;
+    if (!xr) fx = 0.0f;
+    if (!yr) fy = 0.0f;
+    const int x1 = x0 + 1, y1 = y0 + 1;
+    const bool vx0 = x0 >= 0 && x0 < W, vx1 = x1 >= 0 && x1 < W;
+    const bool vy0 = y0 >= 0 && y0 < H, vy1 = y1 >= 0 && y1 < H;
+    const float wx0 = vx0 ? 1.0f - fx : 0.0f, wx1 = vx1 ? fx : 0.0f;
+    const float wy0 = vy0 ? 1.0f - fy : 0.0f, wy1 = vy1 ? fy : 0.0f;
+    const int x0c = min(max(x0, 0), W - 1), x1c = min(max(x1, 0), W - 1);
+    const int y0c = min(max(y0, 0), H - 1), y1c = min(max(y1, 0), H - 1);
+    const uint32_t flags = (vx0 ? 1u : 0u) | (vx1 ? 2u : 0u) | (vy0 ? 4u : 0u) | (vy1 ? 8u : 0u);
+    const uint32_t r = rec_slot<G, NG>(li, g) * 16u;
+    sts128(rec_w + r, make_uint4(__float_as_uint(wx0), __float_as_uint(wx1), __float_as_uint(wy0), __float_as_uint(wy1)));
+    sts128(rec_p + r, make_uint4((uint32_t)(y0c * W + x0c) | (flags << 28), (uint32_t)(y0c * W + x1c),
+                                 (uint32_t)(y1c * W + x0c), (uint32_t)(y1c * W + x1c)));
+}
+
+// The four corner rows of a sample against a query-side vector `qv` (q or dout):
+// dots[c] = partial (this lane's slice) of qv . row_c, as a pair to be summed, and, if
+// WANT_INTERP, interp = sum_c w_c row_c.
+template <typename T, int D, bool STAGED, bool WANT_INTERP>
+__device__ __forceinline__ void corner_dots(const MapReader<T, D, STAGED>& map, const int (&pix)[4], const float2 (&w2)[4],
+                                            int li, const float2 (&qv)[RowCfg<T, D>::EPL / 2],
+                                            float2 (&interp)[RowCfg<T, D>::EPL / 2], float2 (&dots)[4]) {
+    using RC = RowCfg<T, D>;
+    constexpr int HV = RC::EPV / 2;
+    uint4 raw[4][RC::CH];
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int ch = 0; ch < RC::CH; ++ch) raw[c][ch] = map.load(pix[c], ch * RC::G + li);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) dots[c] = make_float2(0.0f, 0.0f);
+#pragma unroll
+    for (int ch = 0; ch < RC::CH; ++ch) {
+        float2 f[4][HV];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) unpack16_pairs(raw[c][ch], f[c], (T*)nullptr);
+#pragma unroll
+        for (int e = 0; e < HV; ++e) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) dots[c] = __ffma2_rn(qv[ch * HV + e], f[c][e], dots[c]);
+            if constexpr (WANT_INTERP) {
+                float2 a = __fmul2_rn(w2[3], f[3][e]);
+                a = __ffma2_rn(w2[2], f[2][e], a);
+                a = __ffma2_rn(w2[1], f[1][e], a);
+                interp[ch * HV + e] = __ffma2_rn(w2[0], f[0][e], a);
+            }
+        }
+    }
+}
+
 template <typename T, int D, int NQ, bool STAGED, int MAXT, int MINB>
 __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
     using RC = RowCfg<T, D>;

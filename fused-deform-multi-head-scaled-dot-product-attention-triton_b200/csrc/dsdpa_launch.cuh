@@ -14,7 +14,8 @@ template <typename T>
 cudaError_t launch_forward(const FwdParams& p, const TilePlan& plan, int D, cudaStream_t stream);
 // two_pass: the kernel writes per-sample scalars instead of scattering (pass A)
 template <typename T>
-cudaError_t launch_backward_main(const BwdParams& p, const TilePlan& plan, int D, bool two_pass, cudaStream_t stream);
+cudaError_t launch_backward_main(const BwdParams& p, const TilePlan& plan, int D, bool two_pass, bool dcoords,
+                                 cudaStream_t stream);
 template <typename T>
 cudaError_t launch_backward_gather(const GatherParams& p, const GatherPlan& plan, int D, cudaStream_t stream);
 template <typename T>
@@ -62,10 +63,10 @@ inline cudaError_t fwd_d(const FwdParams& p, const TilePlan& plan, cudaStream_t 
     }
 }
 
-template <typename T, int D, int NQ, bool STAGED, bool PRIV, bool TWOPASS>
+template <typename T, int D, int NQ, bool STAGED, bool PRIV, bool TWOPASS, bool DCOORDS = false>
 inline cudaError_t bwd_one(const BwdParams& p, const TilePlan& plan, cudaStream_t stream) {
-    auto kern = bwd_scatter_kernel<T, D, NQ, STAGED, PRIV, TWOPASS, STAGED ? kStagedMaxThreads : kL2MaxThreads,
-                                   STAGED ? 1 : 2>;
+    auto kern = bwd_scatter_kernel<T, D, NQ, STAGED, PRIV, TWOPASS, DCOORDS,
+                                   STAGED ? kStagedMaxThreads : kL2MaxThreads, STAGED ? 1 : 2>;
     static bool done[64] = {};
     cudaError_t e = allow_big_smem(kern, done);
     if (e != cudaSuccess) return e;
@@ -74,7 +75,17 @@ inline cudaError_t bwd_one(const BwdParams& p, const TilePlan& plan, cudaStream_
 }
 
 template <typename T, int D>
-inline cudaError_t bwd_d(const BwdParams& p, const TilePlan& plan, bool two_pass, cudaStream_t stream) {
+inline cudaError_t bwd_d(const BwdParams& p, const TilePlan& plan, bool two_pass, bool dcoords, cudaStream_t stream) {
+    if (dcoords) {
+        // the coordinate gradient rides on the two-pass form's first pass
+        if (!two_pass || plan.priv) return cudaErrorInvalidValue;
+        if (!plan.staged) return bwd_one<T, D, 1, false, false, true, true>(p, plan, stream);
+        switch (plan.nq) {
+            case 1: return bwd_one<T, D, 1, true, false, true, true>(p, plan, stream);
+            case 4: return bwd_one<T, D, 4, true, false, true, true>(p, plan, stream);
+            default: return cudaErrorInvalidValue;
+        }
+    }
     if (two_pass) {
         if (plan.priv) return cudaErrorInvalidValue;
         if (!plan.staged) return bwd_one<T, D, 1, false, false, true>(p, plan, stream);

@@ -106,3 +106,64 @@ def test_two_pass_backward_is_bit_reproducible(backend):
     b = _run(backend, (q, k, v, coords, dout), 0x2, cfg.dtype, cfg.W, cfg.H, cfg.sm_scale)
     for x, y in zip(a, b):
         assert torch.equal(x, y)
+
+
+@pytest.mark.parametrize("flagname", ["default", "maps_from_l2"])
+@pytest.mark.parametrize("name", golden_names())
+def test_coordinate_gradient_matches_reference(backend, name, flagname):
+    """The reference's Triton operator returns no gradient for coords (ops/triton.py:464); its
+    PyTorch path does, through grid_sample.  The golden vectors hold that gradient."""
+    c = load_golden(name)
+    dt = c["dtype"]
+    dev = torch.device("cuda", 0)
+    q, k, v, dout = (c[n].to(dev, dt) for n in ("q", "k", "v", "dout"))
+    coords = c["coords"].to(dev)
+    flags = FLAG_SETS[flagname]
+    out, lse = backend.forward_raw(q, k, v, coords, c["W"], c["H"], c["sm_scale"], flags=flags)
+    dq, dk, dv, dc = backend.backward_raw(q, k, v, coords, out, lse, dout, c["W"], c["H"], c["sm_scale"],
+                                          flags=flags, want_dcoords=True)
+    torch.cuda.synchronize()
+    tol = TOL[dt]
+    assert dc.dtype == torch.float32 and dc.shape == coords.shape
+    assert rel_err(dc, c["dcoords"]) < tol
+    # asking for the coordinate gradient does not change the others
+    assert rel_err(dq, c["dq"]) < tol and rel_err(dk, c["dk"]) < tol and rel_err(dv, c["dv"]) < tol
+
+
+def test_autograd_returns_coordinate_gradient(backend):
+    from ops.triton import deform_sdpa_triton
+    c = load_golden("clustered_f32")
+    dev = torch.device("cuda", 0)
+    q, k, v = (c[n].to(dev).requires_grad_(True) for n in ("q", "k", "v"))
+    coords = c["coords"].to(dev).requires_grad_(True)
+    out = deform_sdpa_triton(q, k, v, coords, c["W"], c["H"], c["sm_scale"])
+    out.backward(c["dout"].to(dev))
+    assert coords.grad is not None
+    assert rel_err(coords.grad, c["dcoords"]) < 1e-4
+    assert rel_err(q.grad, c["dq"]) < 1e-4
+
+
+def test_coordinate_gradient_needs_the_two_pass_form(backend):
+    c = load_golden("tiny_f32_uniform")
+    dev = torch.device("cuda", 0)
+    q, k, v, dout = (c[n].to(dev) for n in ("q", "k", "v", "dout"))
+    coords = c["coords"].to(dev)
+    out, lse = backend.forward_raw(q, k, v, coords, c["W"], c["H"], c["sm_scale"])
+    with pytest.raises(ValueError):
+        backend.backward_raw(q, k, v, coords, out, lse, dout, c["W"], c["H"], c["sm_scale"], flags=0x8,
+                             want_dcoords=True)
+
+
+@pytest.mark.parametrize("cfgname", ["C2", "C3"])
+def test_coordinate_gradient_on_configs_against_oracle(backend, oracle, cfgname):
+    from dataclasses import replace
+    cfg = replace(backend.inputs.CONFIGS[cfgname], B=1, Hh=2)
+    q, k, v, coords, dout = backend.inputs.make_inputs(cfg)
+    dev = torch.device("cuda", 0)
+    qd, kd, vd, dd = (t.to(dev) for t in (q, k, v, dout))
+    cd = coords.to(dev)
+    out, lse = backend.forward_raw(qd, kd, vd, cd, cfg.W, cfg.H, cfg.sm_scale)
+    _, _, _, dc = backend.backward_raw(qd, kd, vd, cd, out, lse, dd, cfg.W, cfg.H, cfg.sm_scale, want_dcoords=True)
+    _, _, _, dc_ref = oracle.backward(q, k, v, coords, dout, cfg.W, cfg.H, cfg.sm_scale, with_dcoords=True)
+    # for 16-bit storage delta = out.dout uses the rounded out, as in the reference
+    assert rel_err(dc, dc_ref) < TOL[cfg.dtype]
