@@ -8,6 +8,7 @@ reference's name, positional signature and autograd contract
 from . import cabi  # noqa: F401
 from . import inputs  # noqa: F401
 from . import partition  # noqa: F401
+from .host import HostPipeline  # noqa: F401
 from .op import deform_sdpa, deform_sdpa_triton, forward_raw, backward_raw  # noqa: F401
 
-__all__ = ["deform_sdpa_triton", "deform_sdpa", "forward_raw", "backward_raw", "cabi", "inputs", "partition"]
+__all__ = ["deform_sdpa_triton", "deform_sdpa", "forward_raw", "backward_raw", "cabi", "inputs", "partition", "HostPipeline"]

@@ -167,3 +167,18 @@ def test_coordinate_gradient_on_configs_against_oracle(backend, oracle, cfgname)
     _, _, _, dc_ref = oracle.backward(q, k, v, coords, dout, cfg.W, cfg.H, cfg.sm_scale, with_dcoords=True)
     # for 16-bit storage delta = out.dout uses the rounded out, as in the reference
     assert rel_err(dc, dc_ref) < TOL[cfg.dtype]
+
+
+def test_host_pipeline_equals_one_shot_call(backend):
+    """The chunked host-buffer front end gives exactly what the device call gives."""
+    from dataclasses import replace
+    cfg = replace(backend.inputs.CONFIGS["C2"], B=5)
+    q, k, v, coords, dout = backend.inputs.make_inputs(cfg, pin=True)
+    dev = torch.device("cuda", 0)
+    ref = _run(backend, (q, k, v, coords, dout), 0, cfg.dtype, cfg.W, cfg.H, cfg.sm_scale)
+    out, dq, dk, dv = (torch.empty_like(q).pin_memory() for _ in range(4))
+    pipe = backend.HostPipeline(dev, cfg.W, cfg.H, cfg.sm_scale, chunk=2)
+    pipe.run(q, k, v, coords, dout, out=out, dq=dq, dk=dk, dv=dv)
+    torch.cuda.synchronize()
+    assert torch.equal(out, ref[0].cpu())
+    assert torch.equal(dq, ref[2].cpu()) and torch.equal(dk, ref[3].cpu()) and torch.equal(dv, ref[4].cpu())
