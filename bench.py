@@ -45,6 +45,9 @@ def parse_args():
     ap.add_argument("--mode", default="fwdbwd", choices=["fwdbwd", "fwd"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--sweep", action="store_true",
+                    help="the reference's own sweep instead of the benchmark line: views x samples in {2..12}, "
+                         "forward and backward latency and peak memory (reference benchmark.py:16-57)")
     return ap.parse_args()
 
 
@@ -178,12 +181,61 @@ def config_dict(cfg, args, world):
 
 
 # --------------------------------------------------------------------------------------
+# the reference's sweep (role of its benchmark.py)
+# --------------------------------------------------------------------------------------
+def run_sweep():
+    """Views x samples sweep with the reference's defaults (benchmark.py:16-20, 29-31: batch 2,
+    32 heads, head dim 32, 18x18 map, fp32, sm_scale 0.5, V and S in {2,4,...,12}), forward and
+    backward latency (CUDA events, median of 20 after 5 warm-ups) and peak device memory of one
+    call.  One JSON line per (mode, V, S)."""
+    import torch
+    import ops
+    be = ops.backend
+    dev = torch.device("cuda", 0)
+    B, Hh, D, W = 2, 32, 32, 18
+    L = W * W
+    gen = torch.Generator(device=dev).manual_seed(1)
+    for V in (2, 4, 6, 8, 10, 12):
+        for S in (2, 4, 6, 8, 10, 12):
+            q, k, v, do = (torch.randn(B, V, Hh, L, D, device=dev, generator=gen) for _ in range(4))
+            coords = torch.rand(B, V, L, V, S, 2, device=dev, generator=gen)
+            out, lse = be.forward_raw(q, k, v, coords, W, W, 0.5)
+
+            def fwd():
+                return be.forward_raw(q, k, v, coords, W, W, 0.5)
+
+            def bwd():
+                return be.backward_raw(q, k, v, coords, out, lse, do, W, W, 0.5)
+
+            for mode, fn in (("fwd", fwd), ("bwd", bwd)):
+                for _ in range(5):
+                    fn()
+                times = []
+                for _ in range(20):
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record(); fn(); b.record(); b.synchronize()
+                    times.append(a.elapsed_time(b))
+                torch.cuda.synchronize()
+                torch.cuda.reset_peak_memory_stats(dev)
+                base = torch.cuda.memory_allocated(dev)
+                fn()
+                torch.cuda.synchronize()
+                peak = torch.cuda.max_memory_allocated(dev) - base
+                print(json.dumps({"sweep": mode, "V": V, "S": S, "B": B, "heads": Hh, "D": D, "map": f"{W}x{W}",
+                                  "dtype": "f32", "latency_ms": statistics.median(times),
+                                  "peak_extra_MB": peak / 1e6}), flush=True)
+
+
+# --------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.sweep:
+        run_sweep()
         return
 
     import torch
