@@ -182,3 +182,45 @@ def test_host_pipeline_equals_one_shot_call(backend):
     torch.cuda.synchronize()
     assert torch.equal(out, ref[0].cpu())
     assert torch.equal(dq, ref[2].cpu()) and torch.equal(dk, ref[3].cpu()) and torch.equal(dv, ref[4].cpu())
+
+
+EDGE_CASES = [
+    # B, V, Hh, W, H, D, S, dtype, coords range
+    (1, 2, 1, 5, 3, 256, 3, torch.float32, (-0.2, 1.2)),     # widest head dim, fp32: 32 lanes x 2 vectors per row
+    (1, 2, 2, 4, 4, 256, 5, torch.bfloat16, (0.0, 1.0)),
+    (2, 1, 3, 1, 1, 32, 4, torch.float32, (-0.5, 1.5)),      # a single pixel, a single view
+    (1, 3, 2, 1, 7, 16, 1, torch.float16, (0.0, 1.0)),       # one column, one sample per view, narrowest rows
+    (1, 2, 1, 33, 31, 64, 9, torch.bfloat16, (0.0, 1.0)),    # odd everything, several gather tiles
+    (3, 2, 5, 6, 6, 128, 2, torch.float16, (-0.1, 1.1)),
+]
+
+
+@pytest.mark.parametrize("flagname", ["default", "maps_from_l2", "scatter"])
+@pytest.mark.parametrize("case", EDGE_CASES, ids=lambda c: f"B{c[0]}V{c[1]}h{c[2]}_{c[3]}x{c[4]}_D{c[5]}S{c[6]}_{str(c[7])[6:]}")
+def test_edge_shapes_against_oracle(backend, oracle, case, flagname):
+    B, V, Hh, W, H, D, S, dt, (lo, hi) = case
+    g = torch.Generator().manual_seed(B * 1000 + D + S)
+    L = W * H
+    q, k, v, dout = (torch.randn(B, V, Hh, L, D, generator=g).to(dt) for _ in range(4))
+    coords = torch.rand(B, V, L, V, S, 2, generator=g) * (hi - lo) + lo
+    sm = D ** -0.5
+    out, lse, dq, dk, dv = _run(backend, (q, k, v, coords, dout), FLAG_SETS[flagname], dt, W, H, sm)
+    o_ref, _ = oracle.forward(q, k, v, coords, W, H, sm)
+    dq_ref, dk_ref, dv_ref, _ = oracle.backward(q, k, v, coords, dout, W, H, sm)
+    tol = TOL[dt]
+    assert rel_err(out, o_ref) < tol
+    assert rel_err(dq, dq_ref) < tol and rel_err(dk, dk_ref) < tol and rel_err(dv, dv_ref) < tol
+
+
+def test_non_contiguous_inputs_are_accepted(backend):
+    """The reference's forward takes arbitrary strides (ops/triton.py:400-403); here they are
+    made contiguous on the way in."""
+    from ops.triton import deform_sdpa_triton
+    c = load_golden("oob_f32")
+    dev = torch.device("cuda", 0)
+    # build q with the head and view axes swapped in memory
+    q = c["q"].to(dev).transpose(1, 2).contiguous().transpose(1, 2)
+    assert not q.is_contiguous()
+    coords64 = c["coords"].to(dev).double()          # any float dtype is accepted for coords
+    out = deform_sdpa_triton(q, c["k"].to(dev), c["v"].to(dev), coords64, c["W"], c["H"], c["sm_scale"])
+    assert rel_err(out, c["out"]) < 1e-4
