@@ -48,6 +48,9 @@ def parse_args():
     ap.add_argument("--sweep", action="store_true",
                     help="the reference's own sweep instead of the benchmark line: views x samples in {2..12}, "
                          "forward and backward latency and peak memory (reference benchmark.py:16-57)")
+    ap.add_argument("--profile-case", default=None, metavar="CFG:B:MODE[:FLAGS]",
+                    help="run a small case of a configuration (e.g. C5:2:bwd) twice through the C ABI and exit: "
+                         "the command the ncu captures under profiles/ were taken with")
     return ap.parse_args()
 
 
@@ -226,6 +229,31 @@ def run_sweep():
                                   "peak_extra_MB": peak / 1e6}), flush=True)
 
 
+def run_profile_case(spec):
+    """Forward (and backward) of configuration CFG with batch B, twice, for ncu to capture.
+    MODE is fwd or bwd (= forward + backward); FLAGS are DSDPA_FLAG_* bits."""
+    import torch
+    import ops
+    be = ops.backend
+    parts = spec.split(":")
+    cfg = replace(be.inputs.CONFIGS[parts[0]], B=int(parts[1]))
+    mode = parts[2] if len(parts) > 2 else "fwd"
+    flags = int(parts[3], 0) if len(parts) > 3 else 0
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev).manual_seed(1)
+    shape = (cfg.B, cfg.V, cfg.Hh, cfg.L, cfg.D)
+    q, k, v, do = (torch.randn(shape, device=dev, generator=gen).to(cfg.dtype) for _ in range(4))
+    one = replace(cfg, B=1)
+    coords = torch.stack([be.inputs.make_coords(one, torch.Generator().manual_seed(b)) for b in range(cfg.B)]).to(dev)
+    for _ in range(2):
+        out, lse = be.forward_raw(q, k, v, coords, cfg.W, cfg.H, cfg.sm_scale, flags=flags)
+        if mode != "fwd":
+            be.backward_raw(q, k, v, coords, out, lse, do, cfg.W, cfg.H, cfg.sm_scale, flags=flags)
+    torch.cuda.synchronize()
+    be.cabi.check(be.cabi.lib().dsdpa_device_error(0))
+    print("ok")
+
+
 # --------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------
@@ -236,6 +264,9 @@ def main():
         return
     if args.sweep:
         run_sweep()
+        return
+    if args.profile_case:
+        run_profile_case(args.profile_case)
         return
 
     import torch
