@@ -478,7 +478,11 @@ def main():
     roofline = {
         "kernel": "fwd_kernel (forward, one launch per step)",
         "bound": "l2", "achieved": gather_gbs, "peak": l2_peak, "unit": "GB/s", "frac": gather_gbs / l2_peak,
-        "traffic": None,
+        # dram__bytes_read.sum + dram__bytes_write.sum of the forward kernel from the ncu capture on
+        # C5 with B=2 (profiles/c5_b2_kernels_full_set.md: 118.8 MB for 200,704 query-heads), scaled
+        # to this launch by its query-heads: the traffic grows in proportion to the batch
+        "traffic": (118.8e6 / 200704) * qh_rank if cfg.name == "C5" else None,
+        "traffic_unit": "bytes of DRAM traffic per launch (ncu on a B=2 case, scaled by query-heads)",
         "algorithmic_bytes": "K/V gather bytes: query-heads x V*S keys x 8 rows x D x elem_size",
         "peak_source": "L2 read bandwidth measured in this run (32 MB resident buffer, 128-bit loads)",
         "note": ("K/V maps are staged in shared memory, so the gather is served above the L2 roofline; "
