@@ -203,7 +203,63 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
                     float my_gx = 0.0f, my_gy = 0.0f;  // DCOORDS: gradient of sample s0+li
                     __syncwarp();
                     const int cnt = min(G, p.S - s0);
-                    for (int i = 0; i < cnt; ++i) {
+                    // The common case (two-pass form, no coordinate gradient) takes two samples per
+                    // iteration so that their gathers and the four reductions overlap.
+                    constexpr bool PAIRS = TWOPASS && !DCOORDS;
+                    for (int i = 0; PAIRS && i < cnt; i += 2) {
+                        const bool two = i + 1 < cnt;              // same for the whole warp
+                        const int ib = two ? i + 1 : i;
+                        const uint32_t ra = rec_slot<G, NG>(i, g) * 16u, rb = rec_slot<G, NG>(ib, g) * 16u;
+                        const uint4 wa = lds128(rec_w + ra), pa = lds128(rec_p + ra);
+                        const uint4 wb = lds128(rec_w + rb), pb = lds128(rec_p + rb);
+                        const float2 w2a[4] = { make_float2(__uint_as_float(wa.x), __uint_as_float(wa.x)),
+                                                make_float2(__uint_as_float(wa.y), __uint_as_float(wa.y)),
+                                                make_float2(__uint_as_float(wa.z), __uint_as_float(wa.z)),
+                                                make_float2(__uint_as_float(wa.w), __uint_as_float(wa.w)) };
+                        const float2 w2b[4] = { make_float2(__uint_as_float(wb.x), __uint_as_float(wb.x)),
+                                                make_float2(__uint_as_float(wb.y), __uint_as_float(wb.y)),
+                                                make_float2(__uint_as_float(wb.z), __uint_as_float(wb.z)),
+                                                make_float2(__uint_as_float(wb.w), __uint_as_float(wb.w)) };
+                        const int pixa[4] = { (int)pa.x, (int)pa.y, (int)pa.z, (int)pa.w };
+                        const int pixb[4] = { (int)pb.x, (int)pb.y, (int)pb.z, (int)pb.w };
+                        float2 kta[HP], ktb[HP], vta[HP], vtb[HP];
+                        gather_interp<T, D, STAGED>(kmap, pixa, w2a, li, kta);
+                        gather_interp<T, D, STAGED>(kmap, pixb, w2b, li, ktb);
+                        gather_interp<T, D, STAGED>(vmap, pixa, w2a, li, vta);
+                        gather_interp<T, D, STAGED>(vmap, pixb, w2b, li, vtb);
+                        float2 psa = __fmul2_rn(qf[0], kta[0]), psb = __fmul2_rn(qf[0], ktb[0]);
+                        float2 pda = __fmul2_rn(dof[0], vta[0]), pdb = __fmul2_rn(dof[0], vtb[0]);
+#pragma unroll
+                        for (int e = 1; e < HP; ++e) {
+                            psa = __ffma2_rn(qf[e], kta[e], psa);
+                            psb = __ffma2_rn(qf[e], ktb[e], psb);
+                            pda = __ffma2_rn(dof[e], vta[e], pda);
+                            pdb = __ffma2_rn(dof[e], vtb[e], pdb);
+                        }
+                        float sa = psa.x + psa.y, sb = psb.x + psb.y, da = pda.x + pda.y, db = pdb.x + pdb.y;
+#pragma unroll
+                        for (int o = G / 2; o > 0; o >>= 1) {
+                            sa += __shfl_xor_sync(0xffffffffu, sa, o);
+                            sb += __shfl_xor_sync(0xffffffffu, sb, o);
+                            da += __shfl_xor_sync(0xffffffffu, da, o);
+                            db += __shfl_xor_sync(0xffffffffu, db, o);
+                        }
+                        const float pea = fast_exp2(sa - lse);
+                        const float peb = two ? fast_exp2(sb - lse) : 0.0f;   // no second sample: no contribution
+                        const float dsa = pea * (da - delta), dsb = peb * (db - delta);
+                        const float2 dsa2 = make_float2(dsa, dsa), dsb2 = make_float2(dsb, dsb);
+#pragma unroll
+                        for (int e = 0; e < HP; ++e) dq[j][e] = __ffma2_rn(dsb2, ktb[e], __ffma2_rn(dsa2, kta[e], dq[j][e]));
+                        if (i == li) {
+                            my_a = dsa * p.sm_scale;
+                            my_p = pea;
+                        }
+                        if (two && i + 1 == li) {
+                            my_a = dsb * p.sm_scale;
+                            my_p = peb;
+                        }
+                    }
+                    for (int i = 0; !PAIRS && i < cnt; ++i) {
                         const uint32_t r = rec_slot<G, NG>(i, g) * 16u;
                         const uint4 wr = lds128(rec_w + r), pr = lds128(rec_p + r);
                         float w[4];
