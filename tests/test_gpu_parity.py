@@ -224,3 +224,24 @@ def test_non_contiguous_inputs_are_accepted(backend):
     coords64 = c["coords"].to(dev).double()          # any float dtype is accepted for coords
     out = deform_sdpa_triton(q, c["k"].to(dev), c["v"].to(dev), coords64, c["W"], c["H"], c["sm_scale"])
     assert rel_err(out, c["out"]) < 1e-4
+
+
+def test_large_map_falls_back_to_the_scatter_backward(backend, oracle):
+    """A map of more than ~7000 pixels does not fit the index builder's shared memory: the
+    backward then runs the scatter form by itself (and refuses a coordinate gradient)."""
+    B, V, Hh, W, H, D, S = 1, 2, 1, 100, 80, 16, 2
+    g = torch.Generator().manual_seed(5)
+    L = W * H
+    q, k, v, dout = (torch.randn(B, V, Hh, L, D, generator=g) for _ in range(4))
+    coords = torch.rand(B, V, L, V, S, 2, generator=g) * 1.1 - 0.05
+    text = backend.cabi.describe_plan(backend.cabi.Problem(B, V, Hh, W, H, D, S, 0.25, backend.cabi.F32, 0))
+    assert "bwd_scatter[" in text and "bwd_gather" not in text
+    out, lse, dq, dk, dv = _run(backend, (q, k, v, coords, dout), 0, torch.float32, W, H, 0.25)
+    o_ref, _ = oracle.forward(q, k, v, coords, W, H, 0.25)
+    dq_ref, dk_ref, dv_ref, _ = oracle.backward(q, k, v, coords, dout, W, H, 0.25)
+    assert rel_err(out, o_ref) < 1e-4 and rel_err(dq, dq_ref) < 1e-4
+    assert rel_err(dk, dk_ref) < 1e-4 and rel_err(dv, dv_ref) < 1e-4
+    dev = torch.device("cuda", 0)
+    with pytest.raises(ValueError):
+        backend.backward_raw(q.to(dev), k.to(dev), v.to(dev), coords.to(dev), out, lse, dout.to(dev), W, H, 0.25,
+                             want_dcoords=True)
