@@ -140,7 +140,14 @@ GatherPlan plan_gather(const dsdpa_problem& p) {
     qb_max &= ~1ll;  // even, so that every tile's scalars start on a 16-byte boundary
     // entries address a query's row in 16-byte units and a sample's scalars by index, 16 bits each
     while (qb_max > 2 && (qb_max * rowb / 16 > 65535 || qb_max * p.S > 65535)) qb_max -= 2;
-    const size_t index_smem = ((size_t)8 * L + 256) * sizeof(int);
+    size_t index_smem = ((size_t)8 * L + 256) * sizeof(int);
+    {
+        // The index builder scatters 8-byte entries; with many CTAs per SM their half-written
+        // 32-byte sectors outgrow L2 and are evicted before they are complete.  Asking for more
+        // shared memory than needed caps the CTAs per SM at two (measured best).
+        const size_t floor_kb = (size_t)env_int("DSDPA_INDEX_SMEM_KB", 112);
+        if (floor_kb * 1024 > index_smem && floor_kb * 1024 <= (size_t)kPlanSmemMax) index_smem = floor_kb * 1024;
+    }
     if (qb_max < 2 || p.S > 65535 || index_smem > (size_t)kPlanSmemMax) return g;  // ok = false
     const int force_qb = env_int("DSDPA_GATHER_QB", 0);
     if (force_qb >= 2 && force_qb <= qb_max) qb_max = force_qb & ~1;
