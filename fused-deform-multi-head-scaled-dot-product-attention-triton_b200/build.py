@@ -45,7 +45,8 @@ def _compile(src: Path, force: bool, hdr_time: float) -> Path:
     obj = OBJ / (src.stem + ".o")
     if not force and obj.exists() and obj.stat().st_mtime >= max(src.stat().st_mtime, hdr_time):
         return obj
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    extra = os.environ.get("DSDPA_NVCC_EXTRA", "").split()   # e.g. -DDSDPA_FWD_UNROLL=4, for experiments
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
     res = subprocess.run(cmd, capture_output=True, text=True)
     (OBJ / (src.stem + ".ptxas.log")).write_text(res.stderr)
     if res.returncode != 0:

@@ -71,7 +71,8 @@ TilePlan plan_tiles(const dsdpa_problem& p, bool backward, bool allow_priv) {
         const bool want_priv = backward && allow_priv && !(p.flags & DSDPA_FLAG_SCATTER_GLOBAL) &&
                                smem_need(1, 8, true) <= kPlanSmemMax;
         double best_cost = 1e300;
-        const int nqs_fwd[3] = { 4, 2, 1 }, nqs_bwd[2] = { 4, 1 };
+        // forward: four samples per inner iteration leave registers for two query slots per group
+        const int nqs_fwd[3] = { 2, 1, 1 }, nqs_bwd[2] = { 4, 1 };
         const int* nqs = backward ? nqs_bwd : nqs_fwd;
         const int n_nq = backward ? 2 : 3;
         for (int qi = 0; qi < n_nq; ++qi) {

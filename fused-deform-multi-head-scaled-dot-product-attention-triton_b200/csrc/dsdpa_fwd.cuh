@@ -22,6 +22,11 @@
 
 #include "dsdpa_common.cuh"
 
+// samples handled per iteration of the forward kernel's inner loop
+#ifndef DSDPA_FWD_UNROLL
+#define DSDPA_FWD_UNROLL 4
+#endif
+
 namespace dsdpa {
 
 struct FwdParams {
@@ -279,44 +284,43 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
                     publish_record<G, NG>(cptr, s0 + li, p.S, p.W, p.H, p.hw, p.hh, rec_w, rec_p, li, g);
                     __syncwarp();
                     const int cnt = min(G, p.S - s0);
-                    // two samples per iteration: their gathers and dot-product reductions overlap, and
-                    // the running maximum is updated once for the pair
-                    for (int i = 0; i < cnt; i += 2) {
-                        const bool two = i + 1 < cnt;              // same for the whole warp
-                        const int ib = two ? i + 1 : i;
-                        const uint32_t ra = rec_slot<G, NG>(i, g) * 16u, rb = rec_slot<G, NG>(ib, g) * 16u;
-                        const uint4 wa = lds128(rec_w + ra), pa = lds128(rec_p + ra);
-                        const uint4 wb = lds128(rec_w + rb), pb = lds128(rec_p + rb);
-                        const float2 w2a[4] = { make_float2(__uint_as_float(wa.x), __uint_as_float(wa.x)),
-                                                make_float2(__uint_as_float(wa.y), __uint_as_float(wa.y)),
-                                                make_float2(__uint_as_float(wa.z), __uint_as_float(wa.z)),
-                                                make_float2(__uint_as_float(wa.w), __uint_as_float(wa.w)) };
-                        const float2 w2b[4] = { make_float2(__uint_as_float(wb.x), __uint_as_float(wb.x)),
-                                                make_float2(__uint_as_float(wb.y), __uint_as_float(wb.y)),
-                                                make_float2(__uint_as_float(wb.z), __uint_as_float(wb.z)),
-                                                make_float2(__uint_as_float(wb.w), __uint_as_float(wb.w)) };
-                        const int pixa[4] = { (int)pa.x, (int)pa.y, (int)pa.z, (int)pa.w };
-                        const int pixb[4] = { (int)pb.x, (int)pb.y, (int)pb.z, (int)pb.w };
-                        float2 kta[HP], ktb[HP];
-                        gather_interp<T, D, STAGED>(kmap, pixa, w2a, li, kta);
-                        gather_interp<T, D, STAGED>(kmap, pixb, w2b, li, ktb);
-                        float2 parta = __fmul2_rn(qf[0], kta[0]), partb = __fmul2_rn(qf[0], ktb[0]);
+                    // U samples per iteration: their gathers and dot-product reductions overlap, and
+                    // the running maximum is updated once for the batch
+                    constexpr int U = DSDPA_FWD_UNROLL;
+                    for (int i = 0; i < cnt; i += U) {
+                        float2 w2[U][4];
+                        int pix[U][4];
 #pragma unroll
-                        for (int e = 1; e < HP; ++e) {
-                            parta = __ffma2_rn(qf[e], kta[e], parta);
-                            partb = __ffma2_rn(qf[e], ktb[e], partb);
+                        for (int u = 0; u < U; ++u) {
+                            const int iu = min(i + u, cnt - 1);     // a repeat of the last sample is ignored below
+                            const uint32_t r = rec_slot<G, NG>(iu, g) * 16u;
+                            const uint4 wr = lds128(rec_w + r), pr = lds128(rec_p + r);
+                            w2[u][0] = make_float2(__uint_as_float(wr.x), __uint_as_float(wr.x));
+                            w2[u][1] = make_float2(__uint_as_float(wr.y), __uint_as_float(wr.y));
+                            w2[u][2] = make_float2(__uint_as_float(wr.z), __uint_as_float(wr.z));
+                            w2[u][3] = make_float2(__uint_as_float(wr.w), __uint_as_float(wr.w));
+                            pix[u][0] = (int)pr.x; pix[u][1] = (int)pr.y; pix[u][2] = (int)pr.z; pix[u][3] = (int)pr.w;
                         }
-                        float sa = parta.x + parta.y, sb = partb.x + partb.y;
+                        float sc[U];
 #pragma unroll
-                        for (int o = G / 2; o > 0; o >>= 1) {
-                            sa += __shfl_xor_sync(0xffffffffu, sa, o);
-                            sb += __shfl_xor_sync(0xffffffffu, sb, o);
+                        for (int u = 0; u < U; ++u) {
+                            float2 kt[HP];
+                            gather_interp<T, D, STAGED>(kmap, pix[u], w2[u], li, kt);
+                            float2 part = __fmul2_rn(qf[0], kt[0]);
+#pragma unroll
+                            for (int e = 1; e < HP; ++e) part = __ffma2_rn(qf[e], kt[e], part);
+                            sc[u] = part.x + part.y;
                         }
-                        if (!two) sb = -INFINITY;                  // the pair's second half does not exist
-                        float2 vta[HP], vtb[HP];
-                        gather_interp<T, D, STAGED>(vmap, pixa, w2a, li, vta);
-                        gather_interp<T, D, STAGED>(vmap, pixb, w2b, li, vtb);
-                        const float smax = fmaxf(sa, sb);
+#pragma unroll
+                        for (int o = G / 2; o > 0; o >>= 1)
+#pragma unroll
+                            for (int u = 0; u < U; ++u) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], o);
+                        float smax = sc[0];
+#pragma unroll
+                        for (int u = 1; u < U; ++u) {
+                            if (i + u >= cnt) sc[u] = -INFINITY;    // same for the whole warp
+                            smax = fmaxf(smax, sc[u]);
+                        }
                         if (smax > m) {
                             // new running maximum: rescale what has been accumulated so far
                             const float alpha = fast_exp2(m - smax);
@@ -326,12 +330,16 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
                             for (int e = 0; e < HP; ++e) acc[j][e] = __fmul2_rn(acc[j][e], a2);
                             m = smax;
                         }
-                        const float pea = fast_exp2(sa - m), peb = fast_exp2(sb - m);
-                        lsum += pea + peb;
-                        const float2 p2a = make_float2(pea, pea), p2b = make_float2(peb, peb);
 #pragma unroll
-                        for (int e = 0; e < HP; ++e)
-                            acc[j][e] = __ffma2_rn(p2b, vtb[e], __ffma2_rn(p2a, vta[e], acc[j][e]));
+                        for (int u = 0; u < U; ++u) {
+                            float2 vt[HP];
+                            gather_interp<T, D, STAGED>(vmap, pix[u], w2[u], li, vt);
+                            const float pe = fast_exp2(sc[u] - m);
+                            lsum += pe;
+                            const float2 p2 = make_float2(pe, pe);
+#pragma unroll
+                            for (int e = 0; e < HP; ++e) acc[j][e] = __ffma2_rn(p2, vt[e], acc[j][e]);
+                        }
                     }
                     __syncwarp();
                 }

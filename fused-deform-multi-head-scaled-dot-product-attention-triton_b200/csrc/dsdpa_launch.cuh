@@ -58,7 +58,6 @@ inline cudaError_t fwd_d(const FwdParams& p, const TilePlan& plan, cudaStream_t 
     switch (plan.nq) {
         case 1: return fwd_one<T, D, 1, true>(p, plan, stream);
         case 2: return fwd_one<T, D, 2, true>(p, plan, stream);
-        case 4: return fwd_one<T, D, 4, true>(p, plan, stream);
         default: return cudaErrorInvalidValue;
     }
 }
