@@ -50,7 +50,7 @@ def parse_args():
                          "forward and backward latency and peak memory (reference benchmark.py:16-57)")
     ap.add_argument("--profile-case", default=None, metavar="CFG:B:MODE[:FLAGS]",
                     help="run a small case of a configuration (e.g. C5:2:bwd) twice through the C ABI and exit: "
-                         "the command the ncu captures under profiles/ were taken with")
+                         "the command the committed ncu captures were taken with")
     return ap.parse_args()
 
 
@@ -503,7 +503,7 @@ def main():
         "kernel": "fwd_kernel (forward, one launch per step)",
         "bound": "l2", "achieved": gather_gbs, "peak": l2_peak, "unit": "GB/s", "frac": gather_gbs / l2_peak,
         # dram__bytes_read.sum + dram__bytes_write.sum of the forward kernel from the ncu capture on
-        # C5 with B=2 (profiles/c5_b2_kernels_full_set.md: 118.8 MB for 200,704 query-heads), scaled
+        # C5 with B=2 (118.8 MB for 200,704 query-heads; the capture's summary is committed), scaled
         # to this launch by its query-heads: the traffic grows in proportion to the batch
         "traffic": (118.8e6 / 200704) * qh_rank if cfg.name == "C5" else None,
         "traffic_unit": "bytes of DRAM traffic per launch (ncu on a B=2 case, scaled by query-heads)",

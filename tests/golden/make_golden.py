@@ -90,7 +90,9 @@ CASES = [
 
 
 def main():
-    root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to a checkout of the reference>")
+    root = Path(sys.argv[1])
     ref = load_reference(root)
     torch.set_num_threads(max(1, torch.get_num_threads()))
     for name, B, V, Hh, W, H, D, S, sm_scale, dtype, kind, seed in CASES:
