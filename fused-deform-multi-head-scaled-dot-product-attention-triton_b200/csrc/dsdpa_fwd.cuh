@@ -26,6 +26,10 @@
 #ifndef DSDPA_FWD_UNROLL
 #define DSDPA_FWD_UNROLL 4
 #endif
+// the same for the variant that gathers from L1/L2 (more CTAs per SM, fewer registers each)
+#ifndef DSDPA_FWD_UNROLL_L2
+#define DSDPA_FWD_UNROLL_L2 4
+#endif
 
 namespace dsdpa {
 
@@ -286,7 +290,7 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
                     const int cnt = min(G, p.S - s0);
                     // U samples per iteration: their gathers and dot-product reductions overlap, and
                     // the running maximum is updated once for the batch
-                    constexpr int U = DSDPA_FWD_UNROLL;
+                    constexpr int U = STAGED ? DSDPA_FWD_UNROLL : DSDPA_FWD_UNROLL_L2;
                     for (int i = 0; i < cnt; i += U) {
                         float2 w2[U][4];
                         int pix[U][4];

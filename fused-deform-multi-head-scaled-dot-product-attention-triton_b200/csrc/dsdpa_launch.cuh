@@ -24,6 +24,11 @@ cudaError_t launch_cast_from_f32(const float* src, void* dst, size_t n, cudaStre
 // Thread limits the variants are compiled for (the plan must stay within them).
 constexpr int kStagedMaxThreads = 512;
 constexpr int kL2MaxThreads = 256;
+// CTAs per SM the variants that gather from L1/L2 are compiled for (they hide latency with warps)
+#ifndef DSDPA_L2_MIN_BLOCKS
+#define DSDPA_L2_MIN_BLOCKS 2
+#endif
+constexpr int kL2MinBlocks = DSDPA_L2_MIN_BLOCKS;
 
 namespace detail {
 
@@ -43,7 +48,7 @@ inline cudaError_t allow_big_smem(K kern, bool (&done)[64]) {
 
 template <typename T, int D, int NQ, bool STAGED, int MAXT = (STAGED ? kStagedMaxThreads : kL2MaxThreads)>
 inline cudaError_t fwd_one(const FwdParams& p, const TilePlan& plan, cudaStream_t stream) {
-    auto kern = fwd_kernel<T, D, NQ, STAGED, MAXT, STAGED ? 1 : 2>;
+    auto kern = fwd_kernel<T, D, NQ, STAGED, MAXT, STAGED ? 1 : kL2MinBlocks>;
     if (plan.nw * 32 > MAXT) return cudaErrorInvalidValue;
     static bool done[64] = {};  // a benign race at worst repeats the attribute call
     cudaError_t e = allow_big_smem(kern, done);
@@ -65,7 +70,7 @@ inline cudaError_t fwd_d(const FwdParams& p, const TilePlan& plan, cudaStream_t 
 template <typename T, int D, int NQ, bool STAGED, bool PRIV, bool TWOPASS, bool DCOORDS = false>
 inline cudaError_t bwd_one(const BwdParams& p, const TilePlan& plan, cudaStream_t stream) {
     auto kern = bwd_scatter_kernel<T, D, NQ, STAGED, PRIV, TWOPASS, DCOORDS,
-                                   STAGED ? kStagedMaxThreads : kL2MaxThreads, STAGED ? 1 : 2>;
+                                   STAGED ? kStagedMaxThreads : kL2MaxThreads, STAGED ? 1 : kL2MinBlocks>;
     static bool done[64] = {};
     cudaError_t e = allow_big_smem(kern, done);
     if (e != cudaSuccess) return e;
