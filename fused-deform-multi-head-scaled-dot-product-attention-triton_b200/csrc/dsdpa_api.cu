@@ -160,7 +160,23 @@ GatherPlan plan_gather(const dsdpa_problem& p) {
     g.gather_threads = env_int("DSDPA_GATHER_THREADS", 768);
     if (g.gather_threads < 32 || g.gather_threads > 768 || g.gather_threads % 32) g.gather_threads = 768;
     g.gather_smem = (size_t)qb * 2 * rowb + (((size_t)qb * p.S * 8 + 15) & ~(size_t)15) + 16;
-    g.gather_ctas = (long long)p.B * p.Hh * p.V;
+    // One CTA per SM: when the grid is only a few waves long and the last one is poorly filled,
+    // split every unit's key pixels over 2-4 CTAs.
+    {
+        const long long units = (long long)p.B * p.Hh * p.V;
+        int best = 1;
+        double best_eff = 0.0;
+        for (int ns = 1; ns <= 4; ++ns) {
+            const long long ctas = units * ns;
+            const long long waves = (ctas + kPlanSMs - 1) / kPlanSMs;
+            // every extra CTA of a unit reloads the tiles: charge 2% per split
+            const double eff = (double)ctas / (double)(waves * kPlanSMs) * (1.0 - 0.02 * (ns - 1));
+            if (eff > best_eff + 1e-9) { best_eff = eff; best = ns; }
+        }
+        const int force = env_int("DSDPA_GATHER_NSLAB", 0);
+        g.nslab = force >= 1 && force <= 8 ? force : best;
+        g.gather_ctas = units * g.nslab;
+    }
     const long long T = (long long)p.V * g.tpv;
     g.segments = (long long)p.B * T * p.V;
     g.index_smem = index_smem;
@@ -309,8 +325,8 @@ int dsdpa_describe_plan(const dsdpa_problem* p, char* text, size_t cap) {
     const TilePlan f = plan_tiles(*p, false, false), b = plan_tiles(*p, true, !two);
     char tail[160] = "";
     if (two)
-        std::snprintf(tail, sizeof tail, " bwd_gather[tpv=%d QB=%d ctas=%lld smem=%zu segments=%lld]", g.tpv, g.QB,
-                      g.gather_ctas, g.gather_smem, g.segments);
+        std::snprintf(tail, sizeof tail, " bwd_gather[tpv=%d QB=%d nslab=%d ctas=%lld smem=%zu segments=%lld]", g.tpv, g.QB,
+                      g.nslab, g.gather_ctas, g.gather_smem, g.segments);
     std::snprintf(text, cap,
                   "fwd[%s nstage=%d nw=%d nq=%d tiles=%d q_per_tile=%d ctas=%lld smem=%zu] "
                   "bwd_%s[%s%s nstage=%d nw=%d nq=%d tiles=%d q_per_tile=%d ctas=%lld smem=%zu]%s",
@@ -453,6 +469,7 @@ int dsdpa_backward(const dsdpa_problem* p, const void* q, const void* k, const v
         g.dk32 = dk32; g.dv32 = dv32;
         g.B = p->B; g.V = p->V; g.Hh = p->Hh; g.L = L; g.S = p->S; g.tpv = gp.tpv; g.QB = gp.QB;
         g.seg_entries = gp.seg_entries;
+        g.nslab = gp.nslab;
         g.err = err_word;
         switch (p->dtype) {
             case DSDPA_F32: e = launch_backward_gather<float>(g, gp, p->D, s); break;

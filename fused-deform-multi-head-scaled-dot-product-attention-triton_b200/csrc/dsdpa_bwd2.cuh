@@ -192,6 +192,7 @@ struct GatherParams {
     int B, V, Hh, L, S;
     int tpv, QB;
     int seg_entries;
+    int nslab;            // CTAs per (batch, head, key view)
     int* err;
 };
 
@@ -206,11 +207,15 @@ __global__ void __launch_bounds__(768, 1) bwd_gather_kernel(const GatherParams p
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int g = lane / G, li = lane % G;
-    const int ngroups = nw * NG, gid = warp * NG + g;
+    // (nslab > 1: several CTAs share one (batch, head, key view) and split its key pixels, which
+    // evens out the last wave of a small grid; each still loads every tile)
+    const int slab = blockIdx.x % p.nslab, unit = blockIdx.x / p.nslab;
+    // groups of all CTAs that share the maps, and this group's rank among them
+    const int ngroups = nw * NG * p.nslab, gid = (warp * NG + g) * p.nslab + slab;
     // heads of one (batch, key view) are neighbours in the grid: they share the index
-    const int h = blockIdx.x % p.Hh;
-    const int vk = (blockIdx.x / p.Hh) % p.V;
-    const int b = blockIdx.x / (p.Hh * p.V);
+    const int h = unit % p.Hh;
+    const int vk = (unit / p.Hh) % p.V;
+    const int b = unit / (p.Hh * p.V);
     const int NT = p.V * p.tpv;  // gather tiles per batch element
 
     const uint32_t smem0 = smem_addr(smem);

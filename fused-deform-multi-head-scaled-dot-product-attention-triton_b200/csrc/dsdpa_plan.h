@@ -47,7 +47,8 @@ struct GatherPlan {
     int QB;             // queries (pixels of one query view) per gather tile, even
     int gather_threads;
     size_t gather_smem;
-    long long gather_ctas;   // B*Hh*V
+    int nslab;               // CTAs that split the key pixels of one (batch, head, key view)
+    long long gather_ctas;   // B*Hh*V*nslab
     long long segments;      // B * (V*tpv) * V index segments
     int seg_entries;         // index entries reserved per segment
     size_t index_smem;
