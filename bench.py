@@ -73,7 +73,8 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", os.environ.get("BENCH_CLOCK_MS", "200")], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                text=True)
         except OSError:
             self.proc = None
             return
@@ -288,7 +289,11 @@ def main():
     torch.cuda.set_device(dev)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        # The result gathers share the GPU with kernels that fill every SM: give NCCL's stream
+        # priority, or its CTAs only run in the gaps between kernels and the gather falls behind.
+        opts = dist.ProcessGroupNCCL.Options()
+        opts.is_high_priority_stream = True
+        dist.init_process_group("nccl", device_id=dev, pg_options=opts)
 
     cfg = inp.CONFIGS[args.config]
     plan = part.shard_plan(cfg.B, cfg.Hh, world)
@@ -330,13 +335,29 @@ def main():
     del parts
     full_shape = (cfg.B, cfg.V, cfg.Hh, cfg.L, cfg.D)
 
-    def gather(t):
-        if world == 1:
-            return t
-        return part.gather_to_root(t, plan, full_shape, root=0)
+    # rank 0 receives into the same preallocated tensors every step
+    n_results = 1 if fwd_only else 4
+    dest = [torch.empty(full_shape, dtype=cfg.dtype, device=dev) for _ in range(n_results)] \
+        if world > 1 and rank == 0 else [None] * n_results
 
-    # results travel to rank 0 on their own stream
-    side = torch.cuda.Stream(dev) if world > 1 else None
+    gather_mode = os.environ.get("BENCH_GATHER", "nccl")   # nccl | nccl_sync | peer | none (experiments)
+
+    def gather(t, slot=0):
+        if world == 1 or gather_mode == "none":
+            return t
+        return part.gather_to_root(t, plan, full_shape, root=0, out=dest[slot])
+
+    # results travel to rank 0 on their own stream: by copy engines over NVLink where the ranks
+    # can share memory (one box), else by NCCL
+    side = torch.cuda.Stream(dev) if world > 1 and gather_mode not in ("nccl_sync", "none") else None
+    peer = None
+    if world > 1 and gather_mode == "peer":
+        try:
+            peer = part.PeerGather([(full_shape, cfg.dtype)] * n_results, plan, dev)
+        except Exception as exc:  # noqa: BLE001  (fall back to the NCCL gather)
+            if rank == 0:
+                print(f"peer gather unavailable ({exc!r}); using NCCL", file=sys.stderr)
+            peer = None
 
     ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
     fwd_ms, bwd_ms = [], []
@@ -351,8 +372,12 @@ def main():
             dq, dk, dv, _ = be.backward_raw(q, k, v, coords, out, lse, dout, cfg.W, cfg.H, cfg.sm_scale)
             e2.record()
             res += [dq, dk, dv]
-        if side is None:
-            gathered = [gather(t) for t in res]
+        if peer is not None:
+            for i, t in enumerate(res):
+                peer.push(i, t)
+            gathered = res
+        elif side is None:
+            gathered = [gather(t, i) for i, t in enumerate(res)]
         else:
             # The gathers to rank 0 run on their own stream, behind this step's kernels, and may
             # overlap the next step's kernels; the barrier + synchronize that close the timed
@@ -361,7 +386,7 @@ def main():
             with torch.cuda.stream(side):
                 for t in res:
                     t.record_stream(side)
-                gathered = [gather(t) for t in res]
+                gathered = [gather(t, i) for i, t in enumerate(res)]
         if record:
             fwd_ms.append((e0, e1))
             if not fwd_only:
@@ -389,7 +414,9 @@ def main():
                 a, b = ev(), ev()
                 a.record()
                 fn(True)
-                if side is not None:
+                if peer is not None:
+                    peer.wait()
+                elif side is not None:
                     torch.cuda.current_stream(dev).wait_stream(side)
                 b.record()
                 pairs.append((a, b))
@@ -402,7 +429,9 @@ def main():
         a.record()
         for _ in range(steps):
             fn(True)
-        if side is not None:
+        if peer is not None:
+            peer.wait()
+        elif side is not None:
             # the last steps' gathers belong to the timed region
             torch.cuda.current_stream(dev).wait_stream(side)
         b.record()
@@ -413,11 +442,32 @@ def main():
         return ms.item()
 
     launches0 = lib.dsdpa_kernel_launches()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    sampler = ClockSampler(local_rank) if rank == 0 and os.environ.get("BENCH_CLOCK_MS", "200") != "0" else None
     if sampler:
         sampler.start()
     total_ms = timed(step, args.steps, max(args.warmup, 3))
     clocks = sampler.stop() if sampler else None
+
+    # did the last step's results reach rank 0?  every rank reports the sum of its shard of out;
+    # rank 0 compares with the matching slice of what it received
+    gather_ok = None
+    if world > 1 and gather_mode != "none":
+        last = step(False)
+        if peer is not None:
+            peer.wait()
+        elif side is not None:
+            torch.cuda.current_stream(dev).wait_stream(side)
+        barrier()
+        mine = torch.zeros(world, dtype=torch.float64, device=dev)
+        local_out = last[0][shard.b0:shard.b1] if (peer is None and rank == 0) else None
+        src_out = be.forward_raw(q, k, v, coords, cfg.W, cfg.H, cfg.sm_scale)[0]
+        mine[rank] = src_out.double().sum()
+        dist.all_reduce(mine)
+        if rank == 0:
+            full = peer.results[0] if peer is not None else last[0]
+            got = torch.stack([full[s.b0:s.b1].double().sum() for s in plan])
+            gather_ok = bool(torch.allclose(got, mine, rtol=1e-9, atol=1e-6))
+        del local_out
     launches_all = lib.dsdpa_kernel_launches() - launches0
     cabi.check(lib.dsdpa_device_error(local_rank))
     # launches inside the timed region only (warm-up steps launch the same kernels)
@@ -434,6 +484,9 @@ def main():
     if not fwd_only:
         def fstep(_record):
             out, _lse = be.forward_raw(q, k, v, coords, cfg.W, cfg.H, cfg.sm_scale)
+            if peer is not None:
+                peer.push(0, out)
+                return out
             if side is None:
                 return out
             side.wait_stream(torch.cuda.current_stream(dev))
@@ -549,6 +602,10 @@ def main():
         "gpu_launches": int(launches),
         "clocks": clocks,
         "plan": plan_text,
+        "gather": (None if world == 1 else
+                   {"how": "device-to-device copies into rank 0's tensors over NVLink (CUDA IPC mapping, copy "
+                           "engines)" if peer is not None else "dist.gather over NCCL",
+                    "verified": gather_ok}),
     }
     print(json.dumps(line), flush=True)
     if world > 1:

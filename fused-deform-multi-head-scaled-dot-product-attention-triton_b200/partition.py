@@ -70,10 +70,11 @@ def slice_inputs(shard: Shard, q, k, v, coords, *more):
 
 
 def gather_to_root(local: torch.Tensor, plan: Sequence[Shard], full_shape, root: int = 0,
-                   group=None) -> Optional[torch.Tensor]:
+                   group=None, out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """Gather every rank's ``[b, V, h, L, D]`` shard into the full tensor on ``root``.
 
-    Returns the full tensor on ``root`` and ``None`` elsewhere.  Equal batch shards go
+    Returns the full tensor on ``root`` and ``None`` elsewhere.  ``out`` (root only) is an
+    optional preallocated result, for callers that gather every step.  Equal batch shards go
     through one ``dist.gather`` straight into views of the preallocated result (batch
     shards are contiguous blocks of it); anything else uses point-to-point copies.
     """
@@ -83,7 +84,12 @@ def gather_to_root(local: torch.Tensor, plan: Sequence[Shard], full_shape, root:
         raise ValueError("plan does not match the process group")
     full = None
     if rank == root:
-        full = torch.empty(full_shape, dtype=local.dtype, device=local.device)
+        if out is not None:
+            if tuple(out.shape) != tuple(full_shape) or out.dtype != local.dtype or not out.is_contiguous():
+                raise ValueError("out does not match the full tensor")
+            full = out
+        else:
+            full = torch.empty(full_shape, dtype=local.dtype, device=local.device)
     Hh = full_shape[2]
     batch_only = all(s.h0 == 0 and s.h1 == Hh for s in plan)
     equal = batch_only and len({s.b1 - s.b0 for s in plan}) == 1
@@ -125,3 +131,59 @@ def run_sharded(fn: Callable, q, k, v, coords, *, plan: Sequence[Shard], rank: i
         return None
     qs, ks, vs, cs = slice_inputs(s, q, k, v, coords)
     return fn(qs.contiguous(), ks.contiguous(), vs.contiguous(), cs.contiguous())
+
+
+class PeerGather:
+    """Final gather by copy engines: every rank writes its batch shard straight into the root's
+    result tensors over NVLink with device-to-device copies (no kernel, no SM), on its own stream.
+
+    The kernels of this library fill every SM, so a gather made of NCCL send/recv kernels that
+    runs beside them is starved of SMs; a DMA copy is not.  The root allocates the result
+    tensors once and shares them with the other ranks of the box through CUDA IPC handles
+    (all ranks must be processes on the same machine with peer access between their GPUs).
+    No kernel of the library ever dereferences the peer mapping: it is a copy destination only.
+
+    Usage: ``pg = PeerGather(shapes_and_dtypes, plan, device)``; every step each rank calls
+    ``pg.push(index, shard)`` for its shards (asynchronous, ordered after the current stream);
+    ``pg.wait()`` makes the current stream wait for this rank's copies, and a barrier after it
+    tells the root that everybody's data has landed in ``pg.results`` (root only).
+    """
+
+    def __init__(self, specs, plan: Sequence[Shard], device, root: int = 0, group=None):
+        from torch.multiprocessing.reductions import reduce_tensor
+        self.rank = dist.get_rank(group)
+        self.root = root
+        self.plan = plan
+        self.device = torch.device(device)
+        self.stream = torch.cuda.Stream(self.device)
+        self.group = group
+        Hh = specs[0][0][2]
+        if not all(s.h0 == 0 and s.h1 == Hh for s in plan):
+            raise ValueError("PeerGather handles batch shards (every rank owns all heads)")
+        if self.rank == root:
+            self.results = [torch.empty(shape, dtype=dtype, device=self.device) for shape, dtype in specs]
+            payload = [reduce_tensor(t) for t in self.results]
+        else:
+            self.results = None
+            payload = None
+        box = [payload]
+        dist.broadcast_object_list(box, src=root, group=group)
+        if self.rank == root:
+            self.targets = self.results
+        else:
+            # views of the root's memory in this process
+            self.targets = [fn(*args) for fn, args in box[0]]
+        dist.barrier(group)
+
+    def push(self, index: int, shard: torch.Tensor) -> None:
+        s = self.plan[self.rank]
+        if s.empty:
+            return
+        cur = torch.cuda.current_stream(self.device)
+        self.stream.wait_stream(cur)
+        with torch.cuda.stream(self.stream):
+            shard.record_stream(self.stream)
+            self.targets[index][s.b0:s.b1].copy_(shard, non_blocking=True)
+
+    def wait(self) -> None:
+        torch.cuda.current_stream(self.device).wait_stream(self.stream)
