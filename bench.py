@@ -335,29 +335,37 @@ def main():
     del parts
     full_shape = (cfg.B, cfg.V, cfg.Hh, cfg.L, cfg.D)
 
-    # rank 0 receives into the same preallocated tensors every step
     n_results = 1 if fwd_only else 4
-    dest = [torch.empty(full_shape, dtype=cfg.dtype, device=dev) for _ in range(n_results)] \
-        if world > 1 and rank == 0 else [None] * n_results
 
-    gather_mode = os.environ.get("BENCH_GATHER", "nccl")   # nccl | nccl_sync | peer | none (experiments)
+    # How the results reach rank 0 (inside the timed region in every mode but "none"):
+    #   mirror     the kernels store every result row a second time, into rank 0's tensors, which
+    #              every rank has mapped through CUDA IPC (default; needs all ranks on one box)
+    #   nccl_sync  dist.gather after the step's kernels, on their stream
+    #   nccl       the same on a side stream, free to overlap the next step's kernels
+    #   peer       device-to-device copies into the mapped tensors on a side stream (copy engines)
+    #   none       no gather (to measure what the gather costs)
+    gather_mode = os.environ.get("BENCH_GATHER", "mirror") if world > 1 else "none"
 
     def gather(t, slot=0):
         if world == 1 or gather_mode == "none":
             return t
         return part.gather_to_root(t, plan, full_shape, root=0, out=dest[slot])
 
-    # results travel to rank 0 on their own stream: by copy engines over NVLink where the ranks
-    # can share memory (one box), else by NCCL
-    side = torch.cuda.Stream(dev) if world > 1 and gather_mode not in ("nccl_sync", "none") else None
     peer = None
-    if world > 1 and gather_mode == "peer":
+    if gather_mode in ("peer", "mirror"):
         try:
             peer = part.PeerGather([(full_shape, cfg.dtype)] * n_results, plan, dev)
-        except Exception as exc:  # noqa: BLE001  (fall back to the NCCL gather)
+        except Exception as exc:  # noqa: BLE001  (ranks that cannot share memory gather with NCCL)
             if rank == 0:
-                print(f"peer gather unavailable ({exc!r}); using NCCL", file=sys.stderr)
-            peer = None
+                print(f"rank 0's result tensors cannot be mapped by the other ranks ({exc!r}); using NCCL",
+                      file=sys.stderr)
+            gather_mode = "nccl_sync"
+    side = torch.cuda.Stream(dev) if gather_mode == "nccl" else None
+    # (NCCL modes: rank 0 receives into the same preallocated tensors every step)
+    dest = [torch.empty(full_shape, dtype=cfg.dtype, device=dev) for _ in range(n_results)] \
+        if gather_mode in ("nccl", "nccl_sync") and rank == 0 else [None] * n_results
+    views = peer.shard_views() if gather_mode == "mirror" else None
+    last_local = []
 
     ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
     fwd_ms, bwd_ms = [], []
@@ -365,14 +373,20 @@ def main():
     def step(record):
         e0, e1, e2 = ev(), ev(), ev()
         e0.record()
-        out, lse = be.forward_raw(q, k, v, coords, cfg.W, cfg.H, cfg.sm_scale)
+        out, lse = be.forward_raw(q, k, v, coords, cfg.W, cfg.H, cfg.sm_scale,
+                                  out_mirror=views[0] if views and fwd_only else None)
         e1.record()
         res = [out]
         if not fwd_only:
-            dq, dk, dv, _ = be.backward_raw(q, k, v, coords, out, lse, dout, cfg.W, cfg.H, cfg.sm_scale)
+            # (with mirrors the backward's first pass, which reads out anyway, sends it along)
+            mir = dict(zip(("out", "dq", "dk", "dv"), views)) if views else None
+            dq, dk, dv, _ = be.backward_raw(q, k, v, coords, out, lse, dout, cfg.W, cfg.H, cfg.sm_scale, mirrors=mir)
             e2.record()
             res += [dq, dk, dv]
-        if peer is not None:
+        last_local[:] = res
+        if views is not None:
+            gathered = res
+        elif peer is not None:
             for i, t in enumerate(res):
                 peer.push(i, t)
             gathered = res
@@ -448,8 +462,8 @@ def main():
     total_ms = timed(step, args.steps, max(args.warmup, 3))
     clocks = sampler.stop() if sampler else None
 
-    # did the last step's results reach rank 0?  every rank reports the sum of its shard of out;
-    # rank 0 compares with the matching slice of what it received
+    # did the last step's results reach rank 0?  every rank reports the sum of each of its local
+    # results; rank 0 compares with the matching slices of what it received
     gather_ok = None
     if world > 1 and gather_mode != "none":
         last = step(False)
@@ -458,16 +472,14 @@ def main():
         elif side is not None:
             torch.cuda.current_stream(dev).wait_stream(side)
         barrier()
-        mine = torch.zeros(world, dtype=torch.float64, device=dev)
-        local_out = last[0][shard.b0:shard.b1] if (peer is None and rank == 0) else None
-        src_out = be.forward_raw(q, k, v, coords, cfg.W, cfg.H, cfg.sm_scale)[0]
-        mine[rank] = src_out.double().sum()
+        mine = torch.zeros(n_results, world, dtype=torch.float64, device=dev)
+        for i, t in enumerate(last_local):
+            mine[i, rank] = t.double().sum()
         dist.all_reduce(mine)
         if rank == 0:
-            full = peer.results[0] if peer is not None else last[0]
-            got = torch.stack([full[s.b0:s.b1].double().sum() for s in plan])
+            full = peer.results if peer is not None else last
+            got = torch.stack([torch.stack([f[s.b0:s.b1].double().sum() for s in plan]) for f in full])
             gather_ok = bool(torch.allclose(got, mine, rtol=1e-9, atol=1e-6))
-        del local_out
     launches_all = lib.dsdpa_kernel_launches() - launches0
     cabi.check(lib.dsdpa_device_error(local_rank))
     # launches inside the timed region only (warm-up steps launch the same kernels)
@@ -483,12 +495,15 @@ def main():
     fwd_value = None
     if not fwd_only:
         def fstep(_record):
-            out, _lse = be.forward_raw(q, k, v, coords, cfg.W, cfg.H, cfg.sm_scale)
+            out, _lse = be.forward_raw(q, k, v, coords, cfg.W, cfg.H, cfg.sm_scale,
+                                       out_mirror=views[0] if views else None)
+            if views is not None:
+                return out
             if peer is not None:
                 peer.push(0, out)
                 return out
             if side is None:
-                return out
+                return gather(out)
             side.wait_stream(torch.cuda.current_stream(dev))
             with torch.cuda.stream(side):
                 out.record_stream(side)
@@ -603,8 +618,12 @@ def main():
         "clocks": clocks,
         "plan": plan_text,
         "gather": (None if world == 1 else
-                   {"how": "device-to-device copies into rank 0's tensors over NVLink (CUDA IPC mapping, copy "
-                           "engines)" if peer is not None else "dist.gather over NCCL",
+                   {"how": {"mirror": "the kernels store each result row also into rank 0's tensors over NVLink "
+                                      "(CUDA IPC mapping)",
+                            "peer": "device-to-device copies into rank 0's tensors (CUDA IPC mapping, copy engines)",
+                            "nccl": "dist.gather over NCCL on a side stream",
+                            "nccl_sync": "dist.gather over NCCL after each step's kernels",
+                            "none": "no gather"}[gather_mode],
                     "verified": gather_ok}),
     }
     print(json.dumps(line), flush=True)

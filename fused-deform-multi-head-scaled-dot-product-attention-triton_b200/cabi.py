@@ -41,6 +41,8 @@ EXPORTS = (
     "dsdpa_forward",
     "dsdpa_backward_workspace_bytes",
     "dsdpa_backward",
+    "dsdpa_forward_mirrored",
+    "dsdpa_backward_mirrored",
     "dsdpa_backward_static_scratch",
     "dsdpa_status_string",
     "dsdpa_version",
@@ -61,6 +63,11 @@ class Problem(ctypes.Structure):
         ("W", ctypes.c_int), ("H", ctypes.c_int), ("D", ctypes.c_int), ("S", ctypes.c_int),
         ("sm_scale", ctypes.c_float), ("dtype", ctypes.c_int), ("flags", ctypes.c_uint),
     ]
+
+
+class Mirrors(ctypes.Structure):
+    """Mirror of ``struct dsdpa_mirrors``: second destinations of out, dq, dk, dv (0 = none)."""
+    _fields_ = [("out", ctypes.c_void_p), ("dq", ctypes.c_void_p), ("dk", ctypes.c_void_p), ("dv", ctypes.c_void_p)]
 
 
 class DsdpaError(RuntimeError):
@@ -90,6 +97,10 @@ def lib() -> ctypes.CDLL:
     L.dsdpa_backward_workspace_bytes.restype = ctypes.c_size_t
     L.dsdpa_backward.argtypes = [pp] + [vp] * 11 + [vp, ctypes.c_size_t, ci, vp]
     L.dsdpa_backward.restype = ci
+    L.dsdpa_forward_mirrored.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, ci, vp]
+    L.dsdpa_forward_mirrored.restype = ci
+    L.dsdpa_backward_mirrored.argtypes = [pp] + [vp] * 11 + [vp, ctypes.c_size_t, ctypes.POINTER(Mirrors), ci, vp]
+    L.dsdpa_backward_mirrored.restype = ci
     L.dsdpa_backward_static_scratch.argtypes = [pp] + [vp] * 10 + [ci, vp]
     L.dsdpa_backward_static_scratch.restype = ci
     L.dsdpa_status_string.argtypes = [ci]

@@ -224,6 +224,20 @@ static cudaError_t error_word_ptr(int device, int** out) {
     return cudaSuccess;
 }
 
+// ---- copy of a finished result to its mirror (scatter forms of the backward only) ---
+__global__ void __launch_bounds__(512) copy16_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t n16) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x)
+        stg128(dst + i, ldg128_stream(src + i));
+}
+static cudaError_t launch_copy16(const void* src, void* dst, size_t bytes, cudaStream_t s) {
+    const size_t n16 = bytes / 16;  // results are whole 16-byte rows
+    if (n16 == 0) return cudaSuccess;
+    const size_t want = (n16 + 511) / 512;
+    const unsigned grid = (unsigned)(want < (size_t)kPlanSMs * 4 ? want : (size_t)kPlanSMs * 4);
+    copy16_kernel<<<grid, 512, 0, s>>>((const uint4*)src, (uint4*)dst, n16);
+    return cudaGetLastError();
+}
+
 // ---- bandwidth probes -------------------------------------------------------------
 __device__ unsigned g_probe_sink;  // never read; keeps the probes' loads alive
 
@@ -338,10 +352,16 @@ int dsdpa_describe_plan(const dsdpa_problem* p, char* text, size_t cap) {
 
 int dsdpa_forward(const dsdpa_problem* p, const void* q, const void* k, const void* v, const float* coords,
                   void* out, float* lse, int device, void* stream) {
+    return dsdpa_forward_mirrored(p, q, k, v, coords, out, lse, nullptr, device, stream);
+}
+
+int dsdpa_forward_mirrored(const dsdpa_problem* p, const void* q, const void* k, const void* v, const float* coords,
+                           void* out, float* lse, void* out_mirror, int device, void* stream) {
     int st = validate_problem(p);
     if (st != DSDPA_OK) return st;
     if (!q || !k || !v || !coords || !out || !lse) return DSDPA_ERR_NULL_POINTER;
-    if (misaligned(q) || misaligned(k) || misaligned(v) || misaligned(coords) || misaligned(out) || misaligned(lse))
+    if (misaligned(q) || misaligned(k) || misaligned(v) || misaligned(coords) || misaligned(out) || misaligned(lse) ||
+        misaligned(out_mirror))
         return DSDPA_ERR_MISALIGNED;
     DeviceGuard guard(device);
     if (guard.err != cudaSuccess) return cuda_fail(guard.err);
@@ -351,7 +371,7 @@ int dsdpa_forward(const dsdpa_problem* p, const void* q, const void* k, const vo
 
     const TilePlan plan = plan_tiles(*p, false, false);
     FwdParams fp{};
-    fp.q = q; fp.k = k; fp.v = v; fp.coords = coords; fp.out = out; fp.lse = lse;
+    fp.q = q; fp.k = k; fp.v = v; fp.coords = coords; fp.out = out; fp.out_mirror = out_mirror; fp.lse = lse;
     fp.B = p->B; fp.V = p->V; fp.Hh = p->Hh; fp.W = p->W; fp.H = p->H; fp.L = p->W * p->H; fp.S = p->S;
     fp.scale2 = p->sm_scale * kLog2e;
     fp.hw = (float)(p->W - 1) * 0.5f;
@@ -385,6 +405,16 @@ size_t dsdpa_backward_workspace_bytes(const dsdpa_problem* p) {
 int dsdpa_backward(const dsdpa_problem* p, const void* q, const void* k, const void* v, const float* coords,
                    const void* out, const float* lse, const void* dout, void* dq, void* dk, void* dv,
                    float* dcoords, void* workspace, size_t workspace_bytes, int device, void* stream) {
+    return dsdpa_backward_mirrored(p, q, k, v, coords, out, lse, dout, dq, dk, dv, dcoords, workspace, workspace_bytes,
+                                   nullptr, device, stream);
+}
+
+int dsdpa_backward_mirrored(const dsdpa_problem* p, const void* q, const void* k, const void* v, const float* coords,
+                            const void* out, const float* lse, const void* dout, void* dq, void* dk, void* dv,
+                            float* dcoords, void* workspace, size_t workspace_bytes, const dsdpa_mirrors* mirrors,
+                            int device, void* stream) {
+    const dsdpa_mirrors mir = mirrors ? *mirrors : dsdpa_mirrors{ nullptr, nullptr, nullptr, nullptr };
+    if (misaligned(mir.out) || misaligned(mir.dq) || misaligned(mir.dk) || misaligned(mir.dv)) return DSDPA_ERR_MISALIGNED;
     int st = validate_problem(p);
     if (st != DSDPA_OK) return st;
     if (!q || !k || !v || !coords || !out || !lse || !dout || !dq || !dk || !dv) return DSDPA_ERR_NULL_POINTER;
@@ -440,7 +470,7 @@ int dsdpa_backward(const dsdpa_problem* p, const void* q, const void* k, const v
     const TilePlan plan = plan_tiles(*p, true, !two_pass);
     BwdParams bp{};
     bp.q = q; bp.k = k; bp.v = v; bp.coords = coords; bp.out = out; bp.lse = lse; bp.dout = dout;
-    bp.dq = dq; bp.dk32 = dk32; bp.dv32 = dv32; bp.dcoords = dcoords;
+    bp.dq = dq; bp.out_mirror = mir.out; bp.dq_mirror = mir.dq; bp.dk32 = dk32; bp.dv32 = dv32; bp.dcoords = dcoords;
     bp.B = p->B; bp.V = p->V; bp.Hh = p->Hh; bp.W = p->W; bp.H = p->H; bp.L = L; bp.S = p->S;
     bp.sm_scale = p->sm_scale;
     bp.scale2 = p->sm_scale * kLog2e;
@@ -467,6 +497,7 @@ int dsdpa_backward(const dsdpa_problem* p, const void* q, const void* k, const v
         GatherParams g{};
         g.q = q; g.dout = dout; g.scal = scal; g.rowptr = rowptr; g.entries = entries;
         g.dk32 = dk32; g.dv32 = dv32;
+        g.dk = dk; g.dv = dv; g.dk_mirror = mir.dk; g.dv_mirror = mir.dv;
         g.B = p->B; g.V = p->V; g.Hh = p->Hh; g.L = L; g.S = p->S; g.tpv = gp.tpv; g.QB = gp.QB;
         g.seg_entries = gp.seg_entries;
         g.nslab = gp.nslab;
@@ -480,14 +511,27 @@ int dsdpa_backward(const dsdpa_problem* p, const void* q, const void* k, const v
         g_launches += 1;
     }
 
-    if (p->dtype == DSDPA_BF16) {
-        if ((e = launch_cast_from_f32<__nv_bfloat16>(dk32, dk, n, s)) != cudaSuccess) return cuda_fail(e);
-        if ((e = launch_cast_from_f32<__nv_bfloat16>(dv32, dv, n, s)) != cudaSuccess) return cuda_fail(e);
-        g_launches += 2;
-    } else if (p->dtype == DSDPA_F16) {
-        if ((e = launch_cast_from_f32<__half>(dk32, dk, n, s)) != cudaSuccess) return cuda_fail(e);
-        if ((e = launch_cast_from_f32<__half>(dv32, dv, n, s)) != cudaSuccess) return cuda_fail(e);
-        g_launches += 2;
+    // the gather pass hands the finished maps over itself; the scatter forms need a pass of
+    // their own for the rounding to the storage type and for the mirrors
+    if (!two_pass) {
+        if (p->dtype == DSDPA_BF16) {
+            if ((e = launch_cast_from_f32<__nv_bfloat16>(dk32, dk, n, s)) != cudaSuccess) return cuda_fail(e);
+            if ((e = launch_cast_from_f32<__nv_bfloat16>(dv32, dv, n, s)) != cudaSuccess) return cuda_fail(e);
+            g_launches += 2;
+        } else if (p->dtype == DSDPA_F16) {
+            if ((e = launch_cast_from_f32<__half>(dk32, dk, n, s)) != cudaSuccess) return cuda_fail(e);
+            if ((e = launch_cast_from_f32<__half>(dv32, dv, n, s)) != cudaSuccess) return cuda_fail(e);
+            g_launches += 2;
+        }
+        const size_t bytes = n * dtype_size(p->dtype);
+        if (mir.dk) {
+            if ((e = launch_copy16(dk, mir.dk, bytes, s)) != cudaSuccess) return cuda_fail(e);
+            g_launches += 1;
+        }
+        if (mir.dv) {
+            if ((e = launch_copy16(dv, mir.dv, bytes, s)) != cudaSuccess) return cuda_fail(e);
+            g_launches += 1;
+        }
     }
     return DSDPA_OK;
 }

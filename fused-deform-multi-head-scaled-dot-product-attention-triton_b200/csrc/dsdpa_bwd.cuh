@@ -33,6 +33,8 @@ struct BwdParams {
     const float* lse;
     const void* dout;
     void* dq;
+    void* out_mirror;     // optional: receives a copy of the out rows this kernel reads
+    void* dq_mirror;      // optional second destination of dq
     float* dk32;
     float* dv32;
     float* dcoords;
@@ -128,7 +130,10 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
 #pragma unroll
         for (int ch = 0; ch < CH; ++ch) {
             float fo[EPV], fd[EPV];
-            unpack16(ldg128_nc((const char*)p.out + qrow * ROWB + (size_t)(ch * G + li) * 16), fo, (T*)nullptr);
+            const uint4 oraw = ldg128_nc((const char*)p.out + qrow * ROWB + (size_t)(ch * G + li) * 16);
+            unpack16(oraw, fo, (T*)nullptr);
+            // (slots past the tile's end repeat its last query: the copy is then the same row again)
+            if (p.out_mirror) stg128((char*)p.out_mirror + qrow * ROWB + (size_t)(ch * G + li) * 16, oraw);
             unpack16(ldg128_nc((const char*)p.dout + qrow * ROWB + (size_t)(ch * G + li) * 16), fd, (T*)nullptr);
 #pragma unroll
             for (int e = 0; e < EPV; ++e) part = fmaf(fo[e], fd[e], part);
@@ -419,7 +424,9 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
                 f[2 * e] = dq[j][ch * HV + e].x * p.sm_scale;
                 f[2 * e + 1] = dq[j][ch * HV + e].y * p.sm_scale;
             }
-            stg128((char*)p.dq + qrow * ROWB + (size_t)(ch * G + li) * 16, pack16(f, (T*)nullptr));
+            const uint4 packed = pack16(f, (T*)nullptr);
+            stg128((char*)p.dq + qrow * ROWB + (size_t)(ch * G + li) * 16, packed);
+            if (p.dq_mirror) stg128((char*)p.dq_mirror + qrow * ROWB + (size_t)(ch * G + li) * 16, packed);
         }
     }
 }

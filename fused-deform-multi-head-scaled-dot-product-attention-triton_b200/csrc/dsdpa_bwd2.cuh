@@ -189,12 +189,69 @@ struct GatherParams {
     const uint2* entries;
     float* dk32;
     float* dv32;
+    // where the finished maps go: dk/dv in the storage type (equal to dk32/dv32 for fp32 storage,
+    // which accumulates in place) and the optional mirrors (may be another GPU's memory)
+    void* dk;
+    void* dv;
+    void* dk_mirror;
+    void* dv_mirror;
     int B, V, Hh, L, S;
     int tpv, QB;
     int seg_entries;
     int nslab;            // CTAs per (batch, head, key view)
     int* err;
 };
+
+// After the last tile: a group owns the same key pixels in every tile, and each lane the same
+// elements of their rows, so it hands its finished rows over itself (reading back what it wrote,
+// or the zero fill): rounded to the storage type into dK/dV, and into the mirrors.  These stores
+// are spread over the time the CTAs of the grid finish at.  (Everything it needs is derived
+// again from the block and thread index, so that nothing stays live across the tile loop for it.)
+template <typename T, int D>
+__device__ __forceinline__ void gather_hand_over(const GatherParams& p) {
+    using RC = RowCfg<T, D>;
+    constexpr int G = RC::G, NG = RC::NG, CH = RC::CH, EPV = RC::EPV, ROWB = RC::ROWB;
+    const bool narrow = sizeof(T) == 2;
+    if (!narrow && !p.dk_mirror && !p.dv_mirror) return;
+    // (read through volatile asm: the compiler then derives these values anew instead of
+    // carrying the tile loop's copies in registers through that loop)
+    unsigned tid, cta, ntid;
+    asm volatile("mov.u32 %0, %%tid.x;" : "=r"(tid));
+    asm volatile("mov.u32 %0, %%ctaid.x;" : "=r"(cta));
+    asm volatile("mov.u32 %0, %%ntid.x;" : "=r"(ntid));
+    const int lane = tid & 31, warp = tid >> 5, nw = ntid >> 5;
+    const int g = lane / G, li = lane % G;
+    const int slab = cta % p.nslab, unit = cta / p.nslab;
+    const int ngroups = nw * NG * p.nslab, gid = (warp * NG + g) * p.nslab + slab;
+    const size_t map = (size_t)unit / p.Hh % p.V + (size_t)p.V * (unit / (p.Hh * p.V));  // b*V + vk
+    const size_t map_row0 = (map * p.Hh + unit % p.Hh) * (size_t)p.L;
+    // one map after the other (K, then V) keeps the loop's register need small
+#pragma unroll 1
+    for (int which = 0; which < 2; ++which) {
+        const float* acc = (which ? p.dv32 : p.dk32) + map_row0 * D;
+        void* dst = which ? p.dv : p.dk;
+        void* mir = which ? p.dv_mirror : p.dk_mirror;
+        char* o_loc = narrow ? (char*)dst + map_row0 * ROWB : nullptr;
+        char* o_mir = mir ? (char*)mir + map_row0 * ROWB : nullptr;
+        if (!o_loc && !o_mir) continue;
+#pragma unroll 2
+        for (int pix = gid; pix < p.L; pix += ngroups) {
+#pragma unroll
+            for (int ch = 0; ch < CH; ++ch) {
+                float f[EPV];
+#pragma unroll
+                for (int k = 0; k < EPV / 4; ++k) {
+                    const float4 a = *reinterpret_cast<const float4*>(acc + (size_t)pix * D + (size_t)(ch * G + li) * EPV + 4 * k);
+                    f[4 * k] = a.x; f[4 * k + 1] = a.y; f[4 * k + 2] = a.z; f[4 * k + 3] = a.w;
+                }
+                const uint4 packed = pack16(f, (T*)nullptr);
+                const size_t o = (size_t)pix * ROWB + (size_t)(ch * G + li) * 16;
+                if (o_loc) stg128(o_loc + o, packed);
+                if (o_mir) stg128(o_mir + o, packed);
+            }
+        }
+    }
+}
 
 // Shared memory of one tile: q rows and dout rows in the storage type ([QB, D] each), then
 // the tile's scalars ([QB, S] float2), then the mbarrier; all three filled by bulk copies.
@@ -346,6 +403,8 @@ __global__ void __launch_bounds__(768, 1) bwd_gather_kernel(const GatherParams p
         // every group is done with the tile before its buffers are refilled
         if (__syncthreads_or(ok ? 0 : 1)) return;
     }
+
+    gather_hand_over<T, D>(p);
 }
 
 }  // namespace dsdpa

@@ -39,6 +39,7 @@ struct FwdParams {
     const void* v;
     const float* coords;
     void* out;
+    void* out_mirror;    // optional second destination of out (may be another GPU's memory)
     float* lse;
     int B, V, Hh, W, H, L, S;
     float scale2;        // sm_scale * log2(e)
@@ -378,7 +379,9 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
                 f[2 * e] = acc[j][ch * (EPV / 2) + e].x * inv;
                 f[2 * e + 1] = acc[j][ch * (EPV / 2) + e].y * inv;
             }
-            stg128((char*)p.out + qrow * ROWB + (size_t)(ch * G + li) * 16, pack16(f, (T*)nullptr));
+            const uint4 packed = pack16(f, (T*)nullptr);
+            stg128((char*)p.out + qrow * ROWB + (size_t)(ch * G + li) * 16, packed);
+            if (p.out_mirror) stg128((char*)p.out_mirror + qrow * ROWB + (size_t)(ch * G + li) * 16, packed);
         }
         if (li == 0) p.lse[qrow] = m_run[j] + log2f(l_run[j]);
     }

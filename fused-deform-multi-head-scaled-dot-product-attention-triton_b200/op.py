@@ -58,8 +58,18 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else None
 
 
-def forward_raw(q, k, v, coords, W, H, sm_scale, flags=None):
-    """Forward through the C ABI.  Returns ``(out, lse)``; no autograd."""
+def _check_mirror(name, m, like):
+    if m is None:
+        return
+    if m.shape != like.shape or m.dtype != like.dtype or not m.is_contiguous() or not m.is_cuda:
+        raise ValueError(f"mirror {name!r} must be a contiguous CUDA tensor of shape {tuple(like.shape)} and dtype {like.dtype}")
+
+
+def forward_raw(q, k, v, coords, W, H, sm_scale, flags=None, out_mirror=None):
+    """Forward through the C ABI.  Returns ``(out, lse)``; no autograd.
+
+    ``out_mirror``: a second tensor (same shape and dtype as ``out``; it may live on another GPU
+    whose memory this process has mapped) that the kernel stores every row of ``out`` to as well."""
     flags = default_flags if flags is None else flags
     _check_inputs(q, k, v, coords, W, H)
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
@@ -68,14 +78,19 @@ def forward_raw(q, k, v, coords, W, H, sm_scale, flags=None):
     out = torch.empty_like(q)
     lse = torch.empty(q.shape[:4], device=q.device, dtype=torch.float32)
     stream = torch.cuda.current_stream(q.device).cuda_stream
-    st = cabi.lib().dsdpa_forward(ctypes.byref(prob), _ptr(q), _ptr(k), _ptr(v), _ptr(coords), _ptr(out), _ptr(lse),
-                                  q.device.index, ctypes.c_void_p(stream))
+    _check_mirror("out", out_mirror, out)
+    st = cabi.lib().dsdpa_forward_mirrored(ctypes.byref(prob), _ptr(q), _ptr(k), _ptr(v), _ptr(coords), _ptr(out),
+                                           _ptr(lse), _ptr(out_mirror), q.device.index, ctypes.c_void_p(stream))
     cabi.check(st)
     return out, lse
 
 
-def backward_raw(q, k, v, coords, out, lse, dout, W, H, sm_scale, flags=None, want_dcoords=False):
-    """Backward through the C ABI.  Returns ``(dq, dk, dv, dcoords_or_None)``."""
+def backward_raw(q, k, v, coords, out, lse, dout, W, H, sm_scale, flags=None, want_dcoords=False, mirrors=None):
+    """Backward through the C ABI.  Returns ``(dq, dk, dv, dcoords_or_None)``.
+
+    ``mirrors``: optional dict with any of the keys ``out``, ``dq``, ``dk``, ``dv``: tensors (possibly
+    in another GPU's memory mapped into this process) that receive a second copy of that result
+    (of the ``out`` input, for ``out``), stored by the kernels that produce it."""
     flags = default_flags if flags is None else flags
     q, k, v, out = q.contiguous(), k.contiguous(), v.contiguous(), out.contiguous()
     coords = coords.contiguous().to(torch.float32)
@@ -89,9 +104,19 @@ def backward_raw(q, k, v, coords, out, lse, dout, W, H, sm_scale, flags=None, wa
     ws_bytes = int(L.dsdpa_backward_workspace_bytes(ctypes.byref(prob)))
     ws = torch.empty(max(ws_bytes, 16), device=q.device, dtype=torch.uint8) if ws_bytes else None
     stream = torch.cuda.current_stream(q.device).cuda_stream
-    st = L.dsdpa_backward(ctypes.byref(prob), _ptr(q), _ptr(k), _ptr(v), _ptr(coords), _ptr(out), _ptr(lse), _ptr(dout),
-                          _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dcoords), _ptr(ws), ws_bytes,
-                          q.device.index, ctypes.c_void_p(stream))
+    mir = None
+    if mirrors:
+        unknown = set(mirrors) - {"out", "dq", "dk", "dv"}
+        if unknown:
+            raise ValueError(f"unknown mirrors {sorted(unknown)}")
+        for name, t in mirrors.items():
+            _check_mirror(name, t, q)
+        mir = cabi.Mirrors(*(mirrors[n].data_ptr() if mirrors.get(n) is not None else None
+                             for n in ("out", "dq", "dk", "dv")))
+    st = L.dsdpa_backward_mirrored(ctypes.byref(prob), _ptr(q), _ptr(k), _ptr(v), _ptr(coords), _ptr(out), _ptr(lse),
+                                   _ptr(dout), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dcoords), _ptr(ws), ws_bytes,
+                                   ctypes.byref(mir) if mir is not None else None,
+                                   q.device.index, ctypes.c_void_p(stream))
     cabi.check(st)
     if ws is not None:
         ws.record_stream(torch.cuda.current_stream(q.device))

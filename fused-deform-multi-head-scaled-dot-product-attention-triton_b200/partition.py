@@ -134,19 +134,21 @@ def run_sharded(fn: Callable, q, k, v, coords, *, plan: Sequence[Shard], rank: i
 
 
 class PeerGather:
-    """Final gather by copy engines: every rank writes its batch shard straight into the root's
-    result tensors over NVLink with device-to-device copies (no kernel, no SM), on its own stream.
+    """The root's result tensors, mapped into every rank of the box.
 
-    The kernels of this library fill every SM, so a gather made of NCCL send/recv kernels that
-    runs beside them is starved of SMs; a DMA copy is not.  The root allocates the result
-    tensors once and shares them with the other ranks of the box through CUDA IPC handles
-    (all ranks must be processes on the same machine with peer access between their GPUs).
-    No kernel of the library ever dereferences the peer mapping: it is a copy destination only.
+    The root allocates the full result tensors once and shares them with the other ranks through
+    CUDA IPC handles (all ranks must be processes on one machine with peer access between their
+    GPUs).  ``shard_views()`` returns this rank's batch slice of each of them, in the root's
+    memory: passed as mirrors to ``forward_raw`` / ``backward_raw`` they make the kernels store
+    their rows there as they produce them, so that the job's final gather costs no pass of its
+    own -- the kernels of this library fill every SM, and a gather made of NCCL send/recv kernels
+    beside them is starved of SMs, one behind them adds its full time.  The peer mapping is only
+    ever written, never read.
 
-    Usage: ``pg = PeerGather(shapes_and_dtypes, plan, device)``; every step each rank calls
-    ``pg.push(index, shard)`` for its shards (asynchronous, ordered after the current stream);
-    ``pg.wait()`` makes the current stream wait for this rank's copies, and a barrier after it
-    tells the root that everybody's data has landed in ``pg.results`` (root only).
+    ``push(index, shard)`` is the other way to fill the root's tensors: a device-to-device copy on
+    this object's own stream (copy engines, no SM), ``wait()`` makes the current stream wait for it.
+    Either way a barrier after the last step tells the root that everybody's data has landed in
+    ``results`` (root only).
     """
 
     def __init__(self, specs, plan: Sequence[Shard], device, root: int = 0, group=None):
@@ -174,6 +176,11 @@ class PeerGather:
             # views of the root's memory in this process
             self.targets = [fn(*args) for fn, args in box[0]]
         dist.barrier(group)
+
+    def shard_views(self):
+        """This rank's batch slice of every result tensor of the root (contiguous views)."""
+        s = self.plan[self.rank]
+        return [t[s.b0:s.b1] for t in self.targets]
 
     def push(self, index: int, shard: torch.Tensor) -> None:
         s = self.plan[self.rank]

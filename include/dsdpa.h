@@ -103,6 +103,41 @@ int dsdpa_backward(const dsdpa_problem* p,
                    void* workspace, size_t workspace_bytes, int device, void* stream);
 
 /*
+ * Results stored twice.  (No counterpart in the reference, which runs on one GPU; this is the
+ * partitioner's final gather, ops/triton.py has nothing after its kernels, folded into them.)
+ *
+ * A mirror is a second destination with the layout of the result it shadows.  It may lie in
+ * another GPU's memory that is mapped into this process (CUDA IPC, cuMemMap, a peer-enabled
+ * cudaMalloc): the kernels that produce a result store each row to both places with plain
+ * 16-byte stores, so the transfer to the device that collects a sharded job's results is spread
+ * over the kernels' run time instead of following them as a collective.  Mirrors are only
+ * written, never read.  Any member (or the whole struct pointer) may be NULL; a mirror must be
+ * 16-byte aligned and must not alias an input or a result of the same call.
+ *
+ *   out: written by dsdpa_forward_mirrored; by dsdpa_backward_mirrored it is filled with a copy of
+ *        the `out` INPUT (the first pass reads those rows anyway), so that a forward + backward
+ *        step sends everything from the backward.
+ *   dq, dk, dv: written by dsdpa_backward_mirrored.
+ */
+typedef struct dsdpa_mirrors {
+    void* out;
+    void* dq;
+    void* dk;
+    void* dv;
+} dsdpa_mirrors;
+
+int dsdpa_forward_mirrored(const dsdpa_problem* p,
+                           const void* q, const void* k, const void* v, const float* coords,
+                           void* out, float* lse, void* out_mirror, int device, void* stream);
+
+int dsdpa_backward_mirrored(const dsdpa_problem* p,
+                            const void* q, const void* k, const void* v, const float* coords,
+                            const void* out, const float* lse, const void* dout,
+                            void* dq, void* dk, void* dv, float* dcoords,
+                            void* workspace, size_t workspace_bytes,
+                            const dsdpa_mirrors* mirrors, int device, void* stream);
+
+/*
  * Backward without caller-provided scratch.  (No counterpart in the reference: its backward
  * allocates its accumulators with torch on every call, ops/triton.py:427-430, which is
  * exactly what the callers of this entry point are not allowed to do.)

@@ -245,3 +245,51 @@ def test_large_map_falls_back_to_the_scatter_backward(backend, oracle):
     with pytest.raises(ValueError):
         backend.backward_raw(q.to(dev), k.to(dev), v.to(dev), coords.to(dev), out, lse, dout.to(dev), W, H, 0.25,
                              want_dcoords=True)
+
+
+@pytest.mark.parametrize("flagname", ["default", "scatter", "scatter_global"])
+@pytest.mark.parametrize("name", ["oob_f32", "bf16_d64_clustered", "d16_f16", "d128_f32"])
+def test_mirrors_receive_the_same_bits(backend, name, flagname):
+    """The mirrored entry points store every result a second time (the destination a sharded
+    job gathers into): the copies equal the results bit for bit, results are unchanged by the
+    presence of mirrors, and a missing mirror is simply not written."""
+    c = load_golden(name)
+    dt, flags = c["dtype"], FLAG_SETS[flagname]
+    dev = torch.device("cuda", 0)
+    q, k, v, dout = (c[n].to(dev, dt) for n in ("q", "k", "v", "dout"))
+    coords = c["coords"].to(dev)
+    args = (c["W"], c["H"], c["sm_scale"])
+    out0, lse0 = backend.forward_raw(q, k, v, coords, *args, flags=flags)
+    m_out = torch.full_like(out0, 7.0)
+    out1, lse1 = backend.forward_raw(q, k, v, coords, *args, flags=flags, out_mirror=m_out)
+    assert torch.equal(out0, out1) and torch.equal(lse0, lse1) and torch.equal(m_out, out0)
+
+    mir = {n: torch.full_like(out0, 7.0) for n in ("out", "dq", "dk", "dv")}
+    dq, dk, dv, _ = backend.backward_raw(q, k, v, coords, out0, lse0, dout, *args, flags=flags, mirrors=mir)
+    torch.cuda.synchronize()
+    backend.cabi.check(backend.cabi.lib().dsdpa_device_error(0))
+    assert torch.equal(mir["out"], out0)
+    assert torch.equal(mir["dq"], dq) and torch.equal(mir["dk"], dk) and torch.equal(mir["dv"], dv)
+    tol = TOL[dt]
+    assert rel_err(dq, c["dq"]) < tol and rel_err(dk, c["dk"]) < tol and rel_err(dv, c["dv"]) < tol
+
+    # a subset of mirrors: the others stay untouched
+    only = {"dk": torch.full_like(out0, 7.0)}
+    _, dk2, _, _ = backend.backward_raw(q, k, v, coords, out0, lse0, dout, *args, flags=flags, mirrors=only)
+    if flagname == "default":   # (the scatter forms sum with atomics: not bit-reproducible)
+        assert torch.equal(only["dk"], dk) and torch.equal(dk2, dk)
+    else:
+        assert torch.equal(only["dk"], dk2)
+
+
+def test_mirror_arguments_are_checked(backend):
+    c = load_golden("tiny_f32_uniform")
+    dev = torch.device("cuda", 0)
+    q, k, v = (c[n].to(dev) for n in ("q", "k", "v"))
+    coords = c["coords"].to(dev)
+    with pytest.raises(ValueError):
+        backend.forward_raw(q, k, v, coords, c["W"], c["H"], c["sm_scale"], out_mirror=torch.empty_like(q)[..., :8])
+    out, lse = backend.forward_raw(q, k, v, coords, c["W"], c["H"], c["sm_scale"])
+    with pytest.raises(ValueError):
+        backend.backward_raw(q, k, v, coords, out, lse, c["dout"].to(dev), c["W"], c["H"], c["sm_scale"],
+                             mirrors={"dz": torch.empty_like(q)})
