@@ -23,6 +23,7 @@ ERR_BAD_FLAGS = 7
 ERR_CUDA = 8
 ERR_DEVICE_TIMEOUT = 9
 ERR_TOO_LARGE = 10
+ERR_PEER_ACCESS = 11
 
 # dsdpa_dtype
 F32, BF16, F16 = 0, 1, 2
@@ -36,6 +37,9 @@ FLAG_SCATTER = 0x8
 # limit of dsdpa_backward_static_scratch (DSDPA_STATIC_SCRATCH_BYTES)
 STATIC_SCRATCH_BYTES = 64 << 20
 
+# size of the handle of dsdpa_peer_export / dsdpa_peer_import (DSDPA_PEER_HANDLE_BYTES)
+PEER_HANDLE_BYTES = 64
+
 # Every symbol include/dsdpa.h declares (checked by the CPU test-suite).
 EXPORTS = (
     "dsdpa_forward",
@@ -43,6 +47,9 @@ EXPORTS = (
     "dsdpa_backward",
     "dsdpa_forward_mirrored",
     "dsdpa_backward_mirrored",
+    "dsdpa_peer_export",
+    "dsdpa_peer_import",
+    "dsdpa_peer_release",
     "dsdpa_backward_static_scratch",
     "dsdpa_status_string",
     "dsdpa_version",
@@ -101,6 +108,12 @@ def lib() -> ctypes.CDLL:
     L.dsdpa_forward_mirrored.restype = ci
     L.dsdpa_backward_mirrored.argtypes = [pp] + [vp] * 11 + [vp, ctypes.c_size_t, ctypes.POINTER(Mirrors), ci, vp]
     L.dsdpa_backward_mirrored.restype = ci
+    L.dsdpa_peer_export.argtypes = [vp, ci, ctypes.c_char_p, ctypes.POINTER(ctypes.c_size_t)]
+    L.dsdpa_peer_export.restype = ci
+    L.dsdpa_peer_import.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ci, ctypes.POINTER(vp)]
+    L.dsdpa_peer_import.restype = ci
+    L.dsdpa_peer_release.argtypes = [vp, ctypes.c_size_t, ci]
+    L.dsdpa_peer_release.restype = ci
     L.dsdpa_backward_static_scratch.argtypes = [pp] + [vp] * 10 + [ci, vp]
     L.dsdpa_backward_static_scratch.restype = ci
     L.dsdpa_status_string.argtypes = [ci]
@@ -138,7 +151,7 @@ def check(status: int) -> None:
     if status == ERR_CUDA:
         msg += f" (cudaError {lib().dsdpa_last_cuda_error()})"
         raise DsdpaError(status, msg)
-    if status == ERR_DEVICE_TIMEOUT:
+    if status in (ERR_DEVICE_TIMEOUT, ERR_PEER_ACCESS):
         raise DsdpaError(status, msg)
     if status == ERR_BAD_DTYPE:
         raise NotImplementedError(f"libdeform_sdpa: {msg}")

@@ -210,6 +210,33 @@ struct DeviceGuard {
     }
 };
 
+// A mirror may lie in another GPU's memory: kernels launched on `device` (the current device)
+// must be allowed to store to it, or the first store faults.  Looked up once per pair of devices.
+static int ensure_mirror_access(const void* ptr, int device) {
+    if (!ptr) return DSDPA_OK;
+    cudaPointerAttributes attr{};
+    cudaError_t e = cudaPointerGetAttributes(&attr, ptr);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (attr.type == cudaMemoryTypeHost || attr.type == cudaMemoryTypeManaged) return DSDPA_OK;
+    if (attr.type != cudaMemoryTypeDevice) return DSDPA_ERR_PEER_ACCESS;  // not known to CUDA at all
+    const int owner = attr.device;
+    if (owner == device) return DSDPA_OK;
+    static std::atomic<unsigned char> enabled[64][64];
+    const bool cacheable = device >= 0 && device < 64 && owner >= 0 && owner < 64;
+    if (cacheable && enabled[device][owner].load()) return DSDPA_OK;
+    int can = 0;
+    if ((e = cudaDeviceCanAccessPeer(&can, device, owner)) != cudaSuccess) return cuda_fail(e);
+    if (!can) return DSDPA_ERR_PEER_ACCESS;
+    e = cudaDeviceEnablePeerAccess(owner, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        (void)cudaGetLastError();  // not an error: somebody else switched it on
+        e = cudaSuccess;
+    }
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (cacheable) enabled[device][owner].store(1);
+    return DSDPA_OK;
+}
+
 static cudaError_t error_word_ptr(int device, int** out) {
     static int* cache[64] = {};
     if (device >= 0 && device < 64 && cache[device]) {
@@ -320,6 +347,7 @@ const char* dsdpa_status_string(int status) {
         case DSDPA_ERR_CUDA: return "CUDA runtime error";
         case DSDPA_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel gave up";
         case DSDPA_ERR_TOO_LARGE: return "problem exceeds the maximum of this entry point";
+        case DSDPA_ERR_PEER_ACCESS: return "a mirror lies in memory the launching device cannot store to";
         default: return "unknown status";
     }
 }
@@ -365,6 +393,7 @@ int dsdpa_forward_mirrored(const dsdpa_problem* p, const void* q, const void* k,
         return DSDPA_ERR_MISALIGNED;
     DeviceGuard guard(device);
     if (guard.err != cudaSuccess) return cuda_fail(guard.err);
+    if ((st = ensure_mirror_access(out_mirror, device)) != DSDPA_OK) return st;
     int* err_word = nullptr;
     cudaError_t e = error_word_ptr(device, &err_word);
     if (e != cudaSuccess) return cuda_fail(e);
@@ -426,6 +455,8 @@ int dsdpa_backward_mirrored(const dsdpa_problem* p, const void* q, const void* k
     if (need > 0 && (!workspace || workspace_bytes < need)) return DSDPA_ERR_WORKSPACE;
     DeviceGuard guard(device);
     if (guard.err != cudaSuccess) return cuda_fail(guard.err);
+    for (const void* m : { mir.out, mir.dq, mir.dk, mir.dv })
+        if ((st = ensure_mirror_access(m, device)) != DSDPA_OK) return st;
     int* err_word = nullptr;
     cudaError_t e = error_word_ptr(device, &err_word);
     if (e != cudaSuccess) return cuda_fail(e);
@@ -534,6 +565,49 @@ int dsdpa_backward_mirrored(const dsdpa_problem* p, const void* q, const void* k
         }
     }
     return DSDPA_OK;
+}
+
+int dsdpa_peer_export(const void* ptr, int device, unsigned char handle[DSDPA_PEER_HANDLE_BYTES], size_t* offset) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == DSDPA_PEER_HANDLE_BYTES, "handle size");
+    if (!ptr || !handle || !offset) return DSDPA_ERR_NULL_POINTER;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return cuda_fail(guard.err);
+    // start of the allocation that holds ptr: a driver call, reached through the runtime
+    typedef int (*range_fn)(unsigned long long*, size_t*, unsigned long long);
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult found;
+    cudaError_t e = cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &found);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (!fn || found != cudaDriverEntryPointSuccess) return cuda_fail(cudaErrorNotSupported);
+    unsigned long long base = 0;
+    size_t size = 0;
+    if (((range_fn)fn)(&base, &size, (unsigned long long)(uintptr_t)ptr) != 0) return cuda_fail(cudaErrorInvalidValue);
+    cudaIpcMemHandle_t h;
+    if ((e = cudaIpcGetMemHandle(&h, (void*)(uintptr_t)base)) != cudaSuccess) return cuda_fail(e);
+    std::memcpy(handle, &h, sizeof h);
+    *offset = (size_t)((uintptr_t)ptr - (uintptr_t)base);
+    return DSDPA_OK;
+}
+
+int dsdpa_peer_import(const unsigned char handle[DSDPA_PEER_HANDLE_BYTES], size_t offset, int device, void** ptr) {
+    if (!handle || !ptr) return DSDPA_ERR_NULL_POINTER;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return cuda_fail(guard.err);
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, sizeof h);
+    void* base = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return cuda_fail(e);
+    *ptr = (char*)base + offset;
+    return DSDPA_OK;
+}
+
+int dsdpa_peer_release(void* ptr, size_t offset, int device) {
+    if (!ptr) return DSDPA_ERR_NULL_POINTER;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return cuda_fail(guard.err);
+    cudaError_t e = cudaIpcCloseMemHandle((char*)ptr - offset);
+    return e == cudaSuccess ? DSDPA_OK : cuda_fail(e);
 }
 
 int dsdpa_device_error(int device) {

@@ -133,6 +133,34 @@ def run_sharded(fn: Callable, q, k, v, coords, *, plan: Sequence[Shard], rank: i
     return fn(qs.contiguous(), ks.contiguous(), vs.contiguous(), cs.contiguous())
 
 
+def _numel(shape) -> int:
+    n = 1
+    for d in shape:
+        n *= int(d)
+    return n
+
+
+class _DeviceBytes:
+    """A run of device memory, described the way ``torch.as_tensor`` understands."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def _alias_device_memory(ptr: int, nbytes: int, devices) -> torch.Tensor:
+    """A uint8 tensor over ``[ptr, ptr + nbytes)``.  torch attributes a mapped block either to the
+    device it was mapped on or to the one that owns the memory; naming the wrong one makes
+    ``as_tensor`` copy, so the candidates are tried until the tensor's address is the block's."""
+    for dev in devices:
+        try:
+            t = torch.as_tensor(_DeviceBytes(ptr, nbytes), device=dev)
+        except Exception:  # noqa: BLE001  (a device torch does not accept for this pointer)
+            continue
+        if t.data_ptr() == ptr:
+            return t
+    raise RuntimeError("torch does not alias the mapped block")
+
+
 class PeerGather:
     """The root's result tensors, mapped into every rank of the box.
 
@@ -152,30 +180,68 @@ class PeerGather:
     """
 
     def __init__(self, specs, plan: Sequence[Shard], device, root: int = 0, group=None):
-        from torch.multiprocessing.reductions import reduce_tensor
+        import ctypes
+        from . import cabi
         self.rank = dist.get_rank(group)
         self.root = root
         self.plan = plan
         self.device = torch.device(device)
         self.stream = torch.cuda.Stream(self.device)
         self.group = group
+        self._mapped = None
         Hh = specs[0][0][2]
         if not all(s.h0 == 0 and s.h1 == Hh for s in plan):
             raise ValueError("PeerGather handles batch shards (every rank owns all heads)")
+        # one flat block holds all result tensors: one export, one mapping per process
+        sizes = [(_numel(shape) * torch.empty(0, dtype=dtype).element_size() + 255) // 256 * 256 for shape, dtype in specs]
+        total = sum(sizes)
+        L = cabi.lib()
+        payload, flat, failure = None, None, None
         if self.rank == root:
-            self.results = [torch.empty(shape, dtype=dtype, device=self.device) for shape, dtype in specs]
-            payload = [reduce_tensor(t) for t in self.results]
-        else:
-            self.results = None
-            payload = None
+            try:
+                flat = torch.empty(total, dtype=torch.uint8, device=self.device)
+                handle = ctypes.create_string_buffer(cabi.PEER_HANDLE_BYTES)
+                offset = ctypes.c_size_t()
+                cabi.check(L.dsdpa_peer_export(ctypes.c_void_p(flat.data_ptr()), self.device.index, handle,
+                                               ctypes.byref(offset)))
+                payload = (handle.raw, offset.value, self.device.index)
+            except Exception as exc:  # noqa: BLE001  (reported to every rank below)
+                failure = exc
         box = [payload]
         dist.broadcast_object_list(box, src=root, group=group)
-        if self.rank == root:
-            self.targets = self.results
-        else:
-            # views of the root's memory in this process
-            self.targets = [fn(*args) for fn, args in box[0]]
+        if self.rank != root and box[0] is not None:
+            try:
+                handle, offset, root_device = box[0]
+                ptr = ctypes.c_void_p()
+                # mapped with THIS rank's device current: its kernels are the ones that store there
+                cabi.check(L.dsdpa_peer_import(handle, offset, self.device.index, ctypes.byref(ptr)))
+                self._mapped = (ptr.value, offset)
+                flat = _alias_device_memory(ptr.value, total, (self.device, torch.device("cuda", root_device)))
+            except Exception as exc:  # noqa: BLE001
+                failure = exc
+        # all ranks succeed or all raise (nobody is left waiting in a later collective)
+        ok = torch.tensor([0 if (failure is not None or flat is None) else 1], device=self.device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if ok.item() == 0:
+            self.close()
+            raise RuntimeError(f"the root's result block could not be shared with every rank: {failure!r}")
+        self._flat = flat
+        self.targets, lo = [], 0
+        for (shape, dtype), nbytes in zip(specs, sizes):
+            n = _numel(shape) * torch.empty(0, dtype=dtype).element_size()
+            self.targets.append(flat[lo:lo + n].view(dtype).view(shape))
+            lo += nbytes
+        self.results = self.targets if self.rank == root else None
         dist.barrier(group)
+
+    def close(self) -> None:
+        """Unmap the root's block (non-root ranks).  The views handed out become invalid."""
+        if self._mapped is not None:
+            from . import cabi
+            ptr, offset = self._mapped
+            self._mapped = None
+            self.targets = self._flat = None
+            cabi.lib().dsdpa_peer_release(ptr, offset, self.device.index)
 
     def shard_views(self):
         """This rank's batch slice of every result tensor of the root (contiguous views)."""

@@ -45,7 +45,8 @@ typedef enum dsdpa_status {
     DSDPA_ERR_BAD_FLAGS = 7,
     DSDPA_ERR_CUDA = 8,            /* a CUDA runtime call failed; see dsdpa_last_cuda_error() */
     DSDPA_ERR_DEVICE_TIMEOUT = 9,  /* a bounded wait inside a kernel gave up (dsdpa_device_error) */
-    DSDPA_ERR_TOO_LARGE = 10       /* beyond a stated maximum of the entry point */
+    DSDPA_ERR_TOO_LARGE = 10,      /* beyond a stated maximum of the entry point */
+    DSDPA_ERR_PEER_ACCESS = 11     /* a mirror lies in memory the launching device cannot store to */
 } dsdpa_status;
 
 typedef enum dsdpa_dtype {
@@ -113,6 +114,11 @@ int dsdpa_backward(const dsdpa_problem* p,
  * over the kernels' run time instead of following them as a collective.  Mirrors are only
  * written, never read.  Any member (or the whole struct pointer) may be NULL; a mirror must be
  * 16-byte aligned and must not alias an input or a result of the same call.
+ * Before anything is launched every mirror is looked up (cudaPointerGetAttributes): for one
+ * that lies on another device, peer access from `device` to that device is switched on if it is
+ * not yet (cudaDeviceEnablePeerAccess; it stays on), and a mirror `device` cannot reach is
+ * refused with DSDPA_ERR_PEER_ACCESS.  (Memory mapped with cuMemMap follows cuMemSetAccess
+ * instead: the caller grants `device` write access to it.)
  *
  *   out: written by dsdpa_forward_mirrored; by dsdpa_backward_mirrored it is filled with a copy of
  *        the `out` INPUT (the first pass reads those rows anyway), so that a forward + backward
@@ -136,6 +142,26 @@ int dsdpa_backward_mirrored(const dsdpa_problem* p,
                             void* dq, void* dk, void* dv, float* dcoords,
                             void* workspace, size_t workspace_bytes,
                             const dsdpa_mirrors* mirrors, int device, void* stream);
+
+/*
+ * Sharing a mirror's memory between the processes of one machine (CUDA IPC; plumbing for the
+ * mirrors above, no counterpart in the reference).  Nothing is allocated or freed.
+ *
+ *   dsdpa_peer_export  (owner process) describes the cudaMalloc'd block that holds `ptr`:
+ *       a 64-byte handle of the whole block and the offset of `ptr` inside it.  Send both to
+ *       the other processes by any means.
+ *   dsdpa_peer_import  (other process) maps the block into THIS process for kernels launched on
+ *       `device` -- the mapping is made with `device` current and peer access to the owner's GPU
+ *       is switched on, which a mapping made under another device does not give -- and returns
+ *       the address that corresponds to `ptr`.  Import a block once per process: hand out
+ *       sub-ranges yourself.
+ *   dsdpa_peer_release unmaps what dsdpa_peer_import returned (same offset).  The owner must keep
+ *       the block allocated until every importer has released it.
+ */
+#define DSDPA_PEER_HANDLE_BYTES 64
+int dsdpa_peer_export(const void* ptr, int device, unsigned char handle[DSDPA_PEER_HANDLE_BYTES], size_t* offset);
+int dsdpa_peer_import(const unsigned char handle[DSDPA_PEER_HANDLE_BYTES], size_t offset, int device, void** ptr);
+int dsdpa_peer_release(void* ptr, size_t offset, int device);
 
 /*
  * Backward without caller-provided scratch.  (No counterpart in the reference: its backward

@@ -293,3 +293,26 @@ def test_mirror_arguments_are_checked(backend):
     with pytest.raises(ValueError):
         backend.backward_raw(q, k, v, coords, out, lse, c["dout"].to(dev), c["W"], c["H"], c["sm_scale"],
                              mirrors={"dz": torch.empty_like(q)})
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs with peer access")
+def test_mirrors_in_another_gpus_memory(backend):
+    """Mirrors that lie on a second GPU: the library switches peer access on before it launches,
+    and the kernels' plain stores land there (the path a sharded job's gather takes)."""
+    if not torch.cuda.can_device_access_peer(0, 1):
+        pytest.skip("GPU 0 cannot reach GPU 1")
+    c = load_golden("bf16_d64_clustered")
+    dt = c["dtype"]
+    d0, d1 = torch.device("cuda", 0), torch.device("cuda", 1)
+    q, k, v, dout = (c[n].to(d0, dt) for n in ("q", "k", "v", "dout"))
+    coords = c["coords"].to(d0)
+    args = (c["W"], c["H"], c["sm_scale"])
+    m_out = torch.zeros(q.shape, dtype=dt, device=d1)
+    out, lse = backend.forward_raw(q, k, v, coords, *args, out_mirror=m_out)
+    mir = {n: torch.zeros(q.shape, dtype=dt, device=d1) for n in ("out", "dq", "dk", "dv")}
+    dq, dk, dv, _ = backend.backward_raw(q, k, v, coords, out, lse, dout, *args, mirrors=mir)
+    torch.cuda.synchronize(d0)
+    backend.cabi.check(backend.cabi.lib().dsdpa_device_error(0))
+    assert torch.equal(m_out.to(d0), out) and torch.equal(mir["out"].to(d0), out)
+    for n, t in (("dq", dq), ("dk", dk), ("dv", dv)):
+        assert torch.equal(mir[n].to(d0), t), n
