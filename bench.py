@@ -461,6 +461,7 @@ def main():
         sampler.start()
     total_ms = timed(step, args.steps, max(args.warmup, 3))
     clocks = sampler.stop() if sampler else None
+    launches_all = lib.dsdpa_kernel_launches() - launches0
 
     # did the last step's results reach rank 0?  every rank reports the sum of each of its local
     # results; rank 0 compares with the matching slices of what it received
@@ -480,7 +481,6 @@ def main():
             full = peer.results if peer is not None else last
             got = torch.stack([torch.stack([f[s.b0:s.b1].double().sum() for s in plan]) for f in full])
             gather_ok = bool(torch.allclose(got, mine, rtol=1e-9, atol=1e-6))
-    launches_all = lib.dsdpa_kernel_launches() - launches0
     cabi.check(lib.dsdpa_device_error(local_rank))
     # launches inside the timed region only (warm-up steps launch the same kernels)
     steps_run = args.steps + max(args.warmup, 3)
