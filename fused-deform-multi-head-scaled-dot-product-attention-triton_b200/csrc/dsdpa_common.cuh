@@ -133,6 +133,35 @@ __device__ __forceinline__ void red_shared_add(uint32_t saddr, float a) {
     asm volatile("red.shared.add.f32 [%0], %1;" :: "r"(saddr), "f"(a) : "memory");
 }
 
+// ---- dot products of 16-bit vectors with fp32 accumulation (sm_100 mixed-precision fma) -----
+// fma.rn.f32.{bf16,f16} multiplies two 16-bit operands exactly (8+8 resp. 11+11 mantissa bits fit
+// in fp32) and adds an fp32 accumulator: one instruction per element, against two (unpack, fma) on
+// the fp32 path, and no rounding of the operands.
+__device__ __forceinline__ float fma_mixed(uint16_t a, uint16_t b, float c, __nv_bfloat16*) {
+    float d;
+    asm("fma.rn.f32.bf16 %0, %1, %2, %3;" : "=f"(d) : "h"(a), "h"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float fma_mixed(uint16_t a, uint16_t b, float c, __half*) {
+    float d;
+    asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(d) : "h"(a), "h"(b), "f"(c));
+    return d;
+}
+// acc + sum over the eight 16-bit elements of a and b
+template <typename T>
+__device__ __forceinline__ float dot16(const uint4& a, const uint4& b, float acc) {
+    const uint32_t aw[4] = { a.x, a.y, a.z, a.w }, bw[4] = { b.x, b.y, b.z, b.w };
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint16_t alo, ahi, blo, bhi;
+        asm("mov.b32 {%0, %1}, %2;" : "=h"(alo), "=h"(ahi) : "r"(aw[i]));
+        asm("mov.b32 {%0, %1}, %2;" : "=h"(blo), "=h"(bhi) : "r"(bw[i]));
+        acc = fma_mixed(alo, blo, acc, (T*)nullptr);
+        acc = fma_mixed(ahi, bhi, acc, (T*)nullptr);
+    }
+    return acc;
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

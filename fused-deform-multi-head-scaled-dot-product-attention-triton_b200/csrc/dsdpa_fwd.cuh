@@ -105,6 +105,27 @@ __device__ __forceinline__ void gather_interp(const MapReader<T, D, STAGED>& map
     }
 }
 
+// 16-bit storage: this lane's part of sum_c w_c (qv . row_c) for one sample, the four corner dots
+// taken straight from the stored rows with the mixed-precision fma (no unpack, no interpolated
+// row).  `qv` holds the stored 16-bit query-side row (q or dout), unscaled.
+template <typename T, int D, bool STAGED>
+__device__ __forceinline__ float corner_weighted_dot16(const MapReader<T, D, STAGED>& map, const int (&pix)[4],
+                                                       const float2 (&w2)[4], int li,
+                                                       const uint4 (&qv)[RowCfg<T, D>::CH]) {
+    using RC = RowCfg<T, D>;
+    uint4 raw[4][RC::CH];
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int ch = 0; ch < RC::CH; ++ch) raw[c][ch] = map.load(pix[c], ch * RC::G + li);
+    float d[4] = { 0.0f, 0.0f, 0.0f, 0.0f };
+#pragma unroll
+    for (int ch = 0; ch < RC::CH; ++ch)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) d[c] = dot16<T>(qv[ch], raw[c][ch], d[c]);
+    return fmaf(w2[0].x, d[0], fmaf(w2[1].x, d[1], fmaf(w2[2].x, d[2], w2[3].x * d[3])));
+}
+
 // Decode the sample of this lane and publish its record for the step that consumes it.
 template <int G, int NG>
 __device__ __forceinline__ void publish_record(const float2* cptr, int s, int S, int W, int H, float hw, float hh,
@@ -273,14 +294,22 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
                 const int qi = min(qslot, qend - 1);  // surplus groups redo the last query; never stored
                 const int vq = qi / p.L, l = qi - vq * p.L;
                 const size_t qrow = (((size_t)b * p.V + vq) * p.Hh + h) * p.L + l;
+                // fp32 storage: q in registers as fp32 pairs with the scale folded in; 16-bit storage: the
+                // stored row as it is (the logit's corner dots use the mixed-precision fma, the scale
+                // is applied to the reduced logit)
+                constexpr bool NARROW = sizeof(T) == 2;
                 float2 qf[HP];
+                uint4 qraw[CH];
 #pragma unroll
                 for (int ch = 0; ch < CH; ++ch) {
-                    float2 f[EPV / 2];
-                    unpack16_pairs(ldg128_nc((const char*)p.q + qrow * ROWB + (size_t)(ch * G + li) * 16), f, (T*)nullptr);
+                    qraw[ch] = ldg128_nc((const char*)p.q + qrow * ROWB + (size_t)(ch * G + li) * 16);
+                    if constexpr (!NARROW) {
+                        float2 f[EPV / 2];
+                        unpack16_pairs(qraw[ch], f, (T*)nullptr);
 #pragma unroll
-                    for (int e = 0; e < EPV / 2; ++e)
-                        qf[ch * (EPV / 2) + e] = make_float2(f[e].x * p.scale2, f[e].y * p.scale2);
+                        for (int e = 0; e < EPV / 2; ++e)
+                            qf[ch * (EPV / 2) + e] = make_float2(f[e].x * p.scale2, f[e].y * p.scale2);
+                    }
                 }
                 const float2* cptr = reinterpret_cast<const float2*>(p.coords) +
                                      ((((size_t)b * p.V + vq) * p.L + l) * p.V + vk) * (size_t)p.S;
@@ -309,17 +338,25 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
                         float sc[U];
 #pragma unroll
                         for (int u = 0; u < U; ++u) {
-                            float2 kt[HP];
-                            gather_interp<T, D, STAGED>(kmap, pix[u], w2[u], li, kt);
-                            float2 part = __fmul2_rn(qf[0], kt[0]);
+                            if constexpr (NARROW) {
+                                sc[u] = corner_weighted_dot16<T, D, STAGED>(kmap, pix[u], w2[u], li, qraw);
+                            } else {
+                                float2 kt[HP];
+                                gather_interp<T, D, STAGED>(kmap, pix[u], w2[u], li, kt);
+                                float2 part = __fmul2_rn(qf[0], kt[0]);
 #pragma unroll
-                            for (int e = 1; e < HP; ++e) part = __ffma2_rn(qf[e], kt[e], part);
-                            sc[u] = part.x + part.y;
+                                for (int e = 1; e < HP; ++e) part = __ffma2_rn(qf[e], kt[e], part);
+                                sc[u] = part.x + part.y;
+                            }
                         }
 #pragma unroll
                         for (int o = G / 2; o > 0; o >>= 1)
 #pragma unroll
                             for (int u = 0; u < U; ++u) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], o);
+                        if constexpr (NARROW) {
+#pragma unroll
+                            for (int u = 0; u < U; ++u) sc[u] *= p.scale2;
+                        }
                         float smax = sc[0];
 #pragma unroll
                         for (int u = 1; u < U; ++u) {
