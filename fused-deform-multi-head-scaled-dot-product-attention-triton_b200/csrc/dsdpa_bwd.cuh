@@ -179,13 +179,15 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
                 const int vq = qi / p.L, l = qi - vq * p.L;
                 const size_t qrow = (((size_t)b * p.V + vq) * p.Hh + h) * p.L + l;
                 float2 qf[HP], dof[HP];
+                uint4 doraw[CH];   // the stored dout row (16-bit storage: dout.v~ from corner dots)
 #pragma unroll
                 for (int ch = 0; ch < CH; ++ch) {
                     float2 f[HV];
                     unpack16_pairs(ldg128_nc((const char*)p.q + qrow * ROWB + (size_t)(ch * G + li) * 16), f, (T*)nullptr);
 #pragma unroll
                     for (int e = 0; e < HV; ++e) qf[ch * HV + e] = make_float2(f[e].x * p.scale2, f[e].y * p.scale2);
-                    unpack16_pairs(ldg128_nc((const char*)p.dout + qrow * ROWB + (size_t)(ch * G + li) * 16), f, (T*)nullptr);
+                    doraw[ch] = ldg128_nc((const char*)p.dout + qrow * ROWB + (size_t)(ch * G + li) * 16);
+                    unpack16_pairs(doraw[ch], f, (T*)nullptr);
 #pragma unroll
                     for (int e = 0; e < HV; ++e) dof[ch * HV + e] = f[e];
                 }
@@ -227,21 +229,35 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
                                                 make_float2(__uint_as_float(wb.w), __uint_as_float(wb.w)) };
                         const int pixa[4] = { (int)pa.x, (int)pa.y, (int)pa.z, (int)pa.w };
                         const int pixb[4] = { (int)pb.x, (int)pb.y, (int)pb.z, (int)pb.w };
-                        float2 kta[HP], ktb[HP], vta[HP], vtb[HP];
+                        // k~ is needed as a vector (dq accumulates ds*k~); of v~ only dout.v~, which for
+                        // 16-bit storage comes from the corner dots of the stored rows (mixed-precision
+                        // fma: no unpack, no interpolated row)
+                        float2 kta[HP], ktb[HP];
                         gather_interp<T, D, STAGED>(kmap, pixa, w2a, li, kta);
                         gather_interp<T, D, STAGED>(kmap, pixb, w2b, li, ktb);
-                        gather_interp<T, D, STAGED>(vmap, pixa, w2a, li, vta);
-                        gather_interp<T, D, STAGED>(vmap, pixb, w2b, li, vtb);
                         float2 psa = __fmul2_rn(qf[0], kta[0]), psb = __fmul2_rn(qf[0], ktb[0]);
-                        float2 pda = __fmul2_rn(dof[0], vta[0]), pdb = __fmul2_rn(dof[0], vtb[0]);
 #pragma unroll
                         for (int e = 1; e < HP; ++e) {
                             psa = __ffma2_rn(qf[e], kta[e], psa);
                             psb = __ffma2_rn(qf[e], ktb[e], psb);
-                            pda = __ffma2_rn(dof[e], vta[e], pda);
-                            pdb = __ffma2_rn(dof[e], vtb[e], pdb);
                         }
-                        float sa = psa.x + psa.y, sb = psb.x + psb.y, da = pda.x + pda.y, db = pdb.x + pdb.y;
+                        float sa = psa.x + psa.y, sb = psb.x + psb.y, da, db;
+                        if constexpr (sizeof(T) == 2) {
+                            da = corner_weighted_dot16<T, D, STAGED>(vmap, pixa, w2a, li, doraw);
+                            db = corner_weighted_dot16<T, D, STAGED>(vmap, pixb, w2b, li, doraw);
+                        } else {
+                            float2 vta[HP], vtb[HP];
+                            gather_interp<T, D, STAGED>(vmap, pixa, w2a, li, vta);
+                            gather_interp<T, D, STAGED>(vmap, pixb, w2b, li, vtb);
+                            float2 pda = __fmul2_rn(dof[0], vta[0]), pdb = __fmul2_rn(dof[0], vtb[0]);
+#pragma unroll
+                            for (int e = 1; e < HP; ++e) {
+                                pda = __ffma2_rn(dof[e], vta[e], pda);
+                                pdb = __ffma2_rn(dof[e], vtb[e], pdb);
+                            }
+                            da = pda.x + pda.y;
+                            db = pdb.x + pdb.y;
+                        }
 #pragma unroll
                         for (int o = G / 2; o > 0; o >>= 1) {
                             sa += __shfl_xor_sync(0xffffffffu, sa, o);
