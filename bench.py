@@ -521,7 +521,7 @@ def main():
 
         # the operator's front end for host tensors: chunks of batch elements on three streams
         # (copy in, compute, copy out); every byte still crosses PCIe inside the timed region
-        pipe = be.HostPipeline(dev, cfg.W, cfg.H, cfg.sm_scale, chunk=max(1, min(4, nb)))
+        pipe = be.HostPipeline(dev, cfg.W, cfg.H, cfg.sm_scale, chunk=max(1, min(int(os.environ.get("BENCH_E2E_CHUNK", "8")), nb)))
 
         def estep(_record):
             if fwd_only:

@@ -2,11 +2,12 @@
 
 The reference keeps everything on the device, and so does ``deform_sdpa_triton``.  A caller
 that starts from host tensors pays a host->device copy of q, k, v, coords (and dout) and a
-device->host copy of the results around the kernels.  Batch elements are independent
-(reference ops/triton.py:47-51), so this front end cuts the batch into chunks and runs
-three streams -- copy in, compute, copy out -- so that the PCIe traffic of one chunk hides
-behind the kernels of another.  Results are identical to the one-shot call: the chunks
-are whole batch elements.
+device->host transfer of the results around the kernels.  Batch elements are independent
+(reference ops/triton.py:47-51), so this front end cuts the batch into chunks and overlaps the
+PCIe traffic of one chunk with the kernels of another: inputs by copies on their own stream,
+results by stores of the kernels themselves into pinned host memory (or by copies on a third
+stream when the result tensors are pageable).  Results are identical to the one-shot call: the
+chunks are whole batch elements.
 """
 from __future__ import annotations
 
@@ -17,14 +18,51 @@ import torch
 from .op import backward_raw, forward_raw
 
 
-class HostPipeline:
-    """Forward (+ backward) of the operator on pinned host tensors, chunked over the batch."""
+def chunk_schedule(B: int, chunk: int):
+    """Batch ranges of the pipeline.  The first chunks are small (1, 2, 4, ... batch elements) so
+    that the kernels start after a short first copy, the last ones shrink the same way so that
+    little is left to copy out when the last kernel ends, and the middle runs ``chunk`` elements
+    at a time (large launches are the efficient ones)."""
+    chunk = max(1, int(chunk))
+    ramp, size = [], 1
+    while size < chunk:
+        ramp.append(size)
+        size *= 2
+    while ramp and 2 * sum(ramp) > B:
+        ramp.pop()
+    middle = B - 2 * sum(ramp)
+    sizes = list(ramp)
+    while middle > 0:
+        n = min(chunk, middle)
+        sizes.append(n)
+        middle -= n
+    sizes += reversed(ramp)
+    out, b0 = [], 0
+    for n in sizes:
+        out.append((b0, b0 + n))
+        b0 += n
+    return out
 
-    def __init__(self, device, W: int, H: int, sm_scale: float, chunk: int = 4, flags: Optional[int] = None):
+
+class HostPipeline:
+    """Forward (+ backward) of the operator on host tensors, chunked over the batch.
+
+    Inputs travel by asynchronous copies on their own stream (q, k, v, coords ahead of dout, which
+    only the backward needs), results by copies on a third stream (out as soon as the forward of
+    its chunk is done).  With ``direct_results=True`` results that are PINNED host tensors are not
+    copied: they are handed to the kernels as mirrors and the kernels store every result row into
+    host memory over PCIe while they run.  That leaves nothing to copy out at the end, but the
+    stores hold the kernels back (C5 on a B200: +4% kernel time), more than the short last copy
+    of the tapered schedule costs, so it is not the default.
+    """
+
+    def __init__(self, device, W: int, H: int, sm_scale: float, chunk: int = 8, flags: Optional[int] = None,
+                 direct_results: bool = False):
         self.device = torch.device(device)
         self.W, self.H, self.sm_scale = int(W), int(H), float(sm_scale)
         self.chunk = max(1, int(chunk))
         self.flags = flags
+        self.direct_results = bool(direct_results)
         self.s_in = torch.cuda.Stream(self.device)
         self.s_comp = torch.cuda.Stream(self.device)
         self.s_out = torch.cuda.Stream(self.device)
@@ -51,33 +89,48 @@ class HostPipeline:
         if backward and (dq is None or dk is None or dv is None):
             raise ValueError("dq, dk, dv host tensors are needed when dout is given")
         B = q.shape[0]
+        results = {"out": out, "dq": dq, "dk": dk, "dv": dv} if backward else {"out": out}
+        # a result the kernels can store to directly: pinned, contiguous, of the inputs' type
+        direct = {n: self.direct_results and t.is_pinned() and t.is_contiguous() and t.dtype == q.dtype
+                  and t.shape == q.shape for n, t in results.items()}
         cur = torch.cuda.current_stream(self.device)
         start = torch.cuda.Event()
         start.record(cur)
         for s in (self.s_in, self.s_comp, self.s_out):
             s.wait_event(start)
-        for b0 in range(0, B, self.chunk):
-            b1 = min(B, b0 + self.chunk)
+        for b0, b1 in chunk_schedule(B, self.chunk):
             with torch.cuda.stream(self.s_in):
-                dq_in, dk_in, dv_in, dc_in, ddo_in = self._to_device((q, k, v, coords, dout), b0, b1)
-                ready = torch.cuda.Event()
-                ready.record(self.s_in)
-            self.s_comp.wait_event(ready)
+                d_q, d_k, d_v, d_c = self._to_device((q, k, v, coords), b0, b1)
+                ready_fwd = torch.cuda.Event()
+                ready_fwd.record(self.s_in)
+                (d_do,) = self._to_device((dout,), b0, b1)
+                ready_bwd = torch.cuda.Event()
+                ready_bwd.record(self.s_in)
+            mirror = {n: results[n][b0:b1] for n in results if direct[n]}
+            copies = []
+            self.s_comp.wait_event(ready_fwd)
             with torch.cuda.stream(self.s_comp):
-                o, lse = forward_raw(dq_in, dk_in, dv_in, dc_in, self.W, self.H, self.sm_scale, flags=self.flags)
-                results = [(out, o)]
+                o, lse = forward_raw(d_q, d_k, d_v, d_c, self.W, self.H, self.sm_scale, flags=self.flags,
+                                     out_mirror=mirror.get("out"))
+                if not direct["out"]:
+                    fwd_done = torch.cuda.Event()
+                    fwd_done.record(self.s_comp)
+                    copies.append((fwd_done, out, o))
                 if backward:
-                    gq, gk, gv, _ = backward_raw(dq_in, dk_in, dv_in, dc_in, o, lse, ddo_in, self.W, self.H,
-                                                 self.sm_scale, flags=self.flags)
-                    results += [(dq, gq), (dk, gk), (dv, gv)]
-                done = torch.cuda.Event()
-                done.record(self.s_comp)
-            self.s_out.wait_event(done)
+                    self.s_comp.wait_event(ready_bwd)
+                    grads = backward_raw(d_q, d_k, d_v, d_c, o, lse, d_do, self.W, self.H, self.sm_scale,
+                                         flags=self.flags,
+                                         mirrors={n: t for n, t in mirror.items() if n != "out"} or None)
+                    bwd_done = torch.cuda.Event()
+                    bwd_done.record(self.s_comp)
+                    copies += [(bwd_done, results[n], g) for n, g in zip(("dq", "dk", "dv"), grads) if not direct[n]]
             with torch.cuda.stream(self.s_out):
-                for host, dev_t in results:
+                for event, host, dev_t in copies:
+                    self.s_out.wait_event(event)
                     dev_t.record_stream(self.s_out)
                     host[b0:b1].copy_(dev_t, non_blocking=True)
-        end = torch.cuda.Event()
-        end.record(self.s_out)
-        cur.wait_event(end)
+        for s in (self.s_comp, self.s_out):
+            end = torch.cuda.Event()
+            end.record(s)
+            cur.wait_event(end)
         return out

@@ -61,15 +61,17 @@ def _ptr(t):
 def _check_mirror(name, m, like):
     if m is None:
         return
-    if m.shape != like.shape or m.dtype != like.dtype or not m.is_contiguous() or not m.is_cuda:
-        raise ValueError(f"mirror {name!r} must be a contiguous CUDA tensor of shape {tuple(like.shape)} and dtype {like.dtype}")
+    if m.shape != like.shape or m.dtype != like.dtype or not m.is_contiguous() or not (m.is_cuda or m.is_pinned()):
+        raise ValueError(f"mirror {name!r} must be a contiguous CUDA (or pinned host) tensor of shape "
+                         f"{tuple(like.shape)} and dtype {like.dtype}")
 
 
 def forward_raw(q, k, v, coords, W, H, sm_scale, flags=None, out_mirror=None):
     """Forward through the C ABI.  Returns ``(out, lse)``; no autograd.
 
     ``out_mirror``: a second tensor (same shape and dtype as ``out``; it may live on another GPU
-    whose memory this process has mapped) that the kernel stores every row of ``out`` to as well."""
+    whose memory this process has mapped, or in pinned host memory) that the kernel stores every
+    row of ``out`` to as well."""
     flags = default_flags if flags is None else flags
     _check_inputs(q, k, v, coords, W, H)
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()

@@ -169,15 +169,19 @@ def test_coordinate_gradient_on_configs_against_oracle(backend, oracle, cfgname)
     assert rel_err(dc, dc_ref) < TOL[cfg.dtype]
 
 
-def test_host_pipeline_equals_one_shot_call(backend):
-    """The chunked host-buffer front end gives exactly what the device call gives."""
+@pytest.mark.parametrize("results", ["pinned", "pinned_direct", "pageable"])
+def test_host_pipeline_equals_one_shot_call(backend, results):
+    """The chunked host-buffer front end gives exactly what the device call gives, whether the
+    kernels store the results into pinned host memory themselves or they are copied out."""
     from dataclasses import replace
     cfg = replace(backend.inputs.CONFIGS["C2"], B=5)
     q, k, v, coords, dout = backend.inputs.make_inputs(cfg, pin=True)
     dev = torch.device("cuda", 0)
     ref = _run(backend, (q, k, v, coords, dout), 0, cfg.dtype, cfg.W, cfg.H, cfg.sm_scale)
-    out, dq, dk, dv = (torch.empty_like(q).pin_memory() for _ in range(4))
-    pipe = backend.HostPipeline(dev, cfg.W, cfg.H, cfg.sm_scale, chunk=2)
+    out, dq, dk, dv = (torch.zeros_like(q) for _ in range(4))
+    if results != "pageable":
+        out, dq, dk, dv = (t.pin_memory() for t in (out, dq, dk, dv))
+    pipe = backend.HostPipeline(dev, cfg.W, cfg.H, cfg.sm_scale, chunk=2, direct_results=results == "pinned_direct")
     pipe.run(q, k, v, coords, dout, out=out, dq=dq, dk=dk, dv=dv)
     torch.cuda.synchronize()
     assert torch.equal(out, ref[0].cpu())
