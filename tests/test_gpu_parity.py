@@ -320,3 +320,32 @@ def test_mirrors_in_another_gpus_memory(backend):
     assert torch.equal(m_out.to(d0), out) and torch.equal(mir["out"].to(d0), out)
     for n, t in (("dq", dq), ("dk", dk), ("dv", dv)):
         assert torch.equal(mir[n].to(d0), t), n
+
+
+def test_a_mirror_the_device_cannot_store_to_is_refused(backend):
+    """A mirror in memory CUDA does not know (pageable host memory) is refused with a status
+    before anything is launched; the results of the call are not produced."""
+    import ctypes
+    import numpy as np
+    cabi = backend.cabi
+    c = load_golden("tiny_f32_uniform")
+    dev = torch.device("cuda", 0)
+    q, k, v = (c[n].to(dev) for n in ("q", "k", "v"))
+    coords = c["coords"].to(dev)
+    B, V, Hh, L, D = q.shape
+    prob = cabi.Problem(B, V, Hh, c["W"], c["H"], D, coords.shape[4], c["sm_scale"], cabi.F32, 0)
+    out = torch.zeros_like(q)
+    lse = torch.zeros(q.shape[:4], device=dev)
+    host = np.zeros(q.numel() + 8, dtype=np.float32)
+    addr = (host.ctypes.data + 15) & ~15
+    before = cabi.lib().dsdpa_kernel_launches()
+    vp = ctypes.c_void_p
+    st = cabi.lib().dsdpa_forward_mirrored(ctypes.byref(prob), vp(q.data_ptr()), vp(k.data_ptr()), vp(v.data_ptr()),
+                                           vp(coords.data_ptr()), vp(out.data_ptr()), vp(lse.data_ptr()), vp(addr),
+                                           0, None)
+    assert st == cabi.ERR_PEER_ACCESS
+    assert cabi.lib().dsdpa_kernel_launches() == before
+    with pytest.raises(cabi.DsdpaError):
+        cabi.check(st)
+    torch.cuda.synchronize()
+    assert not out.any()
