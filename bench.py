@@ -8,7 +8,9 @@ One "step" is one pass of the hot path over the workload: forward and backward
 (dq, dk, dv) of the operator through the C ABI.  The workload at every N is the
 scaling configuration C5 (B=32, V=8, S=32, heads=16, D=64, 28x28 map, bf16, uniform
 coordinates), the total split by batch over the N ranks ("strong" scaling) with the
-outputs gathered to rank 0 inside the timed region.  Rank 0 prints ONE JSON line.
+results landing on rank 0 inside the timed region (by default the kernels store them
+there themselves as they produce them; the environment variable BENCH_GATHER selects the
+other ways, see main).  Rank 0 prints ONE JSON line.
 
 `--impl reference` times the CPU implementation of the same path (the C oracle port of
 the reference's ops/torch.py, all host threads) on a bounded sample of the workload.
