@@ -316,25 +316,33 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
                             sc = group_sum<G>(ps.x + ps.y);
                             dp = group_sum<G>(pd.x + pd.y);
                         } else {
-                            // per-corner dots A_c = qf.K_c (qf carries scale2) and B_c = dout.V_c
-                            float2 ac[4], bc[4], unused[HP];
+                            // per-corner dots A_c = qf.K_c (qf carries scale2) and B_c = dout.V_c, as this
+                            // lane's parts: what is needed of them (logit, dout.v~ and their derivatives
+                            // along x and y) is linear in the dots with coefficients the whole group
+                            // shares, so the six combinations are formed per lane and then summed over
+                            // the group (six reductions instead of eight)
+                            float2 ac[4];
                             corner_dots<T, D, STAGED, true>(kmap, pix, w2, li, qf, kt, ac);
-                            corner_dots<T, D, STAGED, false>(vmap, pix, w2, li, dof, unused, bc);
                             float a4[4], b4[4];
 #pragma unroll
-                            for (int c = 0; c < 4; ++c) {
-                                a4[c] = group_sum<G>(ac[c].x + ac[c].y);
-                                b4[c] = group_sum<G>(bc[c].x + bc[c].y);
+                            for (int c = 0; c < 4; ++c) a4[c] = ac[c].x + ac[c].y;
+                            if constexpr (sizeof(T) == 2) {
+                                corner_dots16<T, D, STAGED>(vmap, pix, li, doraw, b4);
+                            } else {
+                                float2 bc[4], unused[HP];
+                                corner_dots<T, D, STAGED, false>(vmap, pix, w2, li, dof, unused, bc);
+#pragma unroll
+                                for (int c = 0; c < 4; ++c) b4[c] = bc[c].x + bc[c].y;
                             }
-                            sc = w[0] * a4[0] + w[1] * a4[1] + w[2] * a4[2] + w[3] * a4[3];
-                            dp = w[0] * b4[0] + w[1] * b4[1] + w[2] * b4[2] + w[3] * b4[3];
                             // a corner outside the map has value zero: drop its dot
                             const float vx0 = (flags & 1u) ? 1.0f : 0.0f, vx1 = (flags & 2u) ? 1.0f : 0.0f;
                             const float vy0 = (flags & 4u) ? 1.0f : 0.0f, vy1 = (flags & 8u) ? 1.0f : 0.0f;
-                            ax = wy0 * (vx1 * a4[1] - vx0 * a4[0]) + wy1 * (vx1 * a4[3] - vx0 * a4[2]);
-                            ay = wx0 * (vy1 * a4[2] - vy0 * a4[0]) + wx1 * (vy1 * a4[3] - vy0 * a4[1]);
-                            bx = wy0 * (vx1 * b4[1] - vx0 * b4[0]) + wy1 * (vx1 * b4[3] - vx0 * b4[2]);
-                            by = wx0 * (vy1 * b4[2] - vy0 * b4[0]) + wx1 * (vy1 * b4[3] - vy0 * b4[1]);
+                            sc = group_sum<G>(w[0] * a4[0] + w[1] * a4[1] + w[2] * a4[2] + w[3] * a4[3]);
+                            dp = group_sum<G>(w[0] * b4[0] + w[1] * b4[1] + w[2] * b4[2] + w[3] * b4[3]);
+                            ax = group_sum<G>(wy0 * (vx1 * a4[1] - vx0 * a4[0]) + wy1 * (vx1 * a4[3] - vx0 * a4[2]));
+                            ay = group_sum<G>(wx0 * (vy1 * a4[2] - vy0 * a4[0]) + wx1 * (vy1 * a4[3] - vy0 * a4[1]));
+                            bx = group_sum<G>(wy0 * (vx1 * b4[1] - vx0 * b4[0]) + wy1 * (vx1 * b4[3] - vx0 * b4[2]));
+                            by = group_sum<G>(wx0 * (vy1 * b4[2] - vy0 * b4[0]) + wx1 * (vy1 * b4[3] - vy0 * b4[1]));
                         }
                         const float pe = fast_exp2(sc - lse);
                         const float ds = pe * (dp - delta);

@@ -105,24 +105,33 @@ __device__ __forceinline__ void gather_interp(const MapReader<T, D, STAGED>& map
     }
 }
 
-// 16-bit storage: this lane's part of sum_c w_c (qv . row_c) for one sample, the four corner dots
-// taken straight from the stored rows with the mixed-precision fma (no unpack, no interpolated
-// row).  `qv` holds the stored 16-bit query-side row (q or dout), unscaled.
+// 16-bit storage: this lane's parts d[c] of the four corner dots qv . row_c of one sample, taken
+// straight from the stored rows with the mixed-precision fma (no unpack).  `qv` holds the stored
+// 16-bit query-side row (q or dout), unscaled.
 template <typename T, int D, bool STAGED>
-__device__ __forceinline__ float corner_weighted_dot16(const MapReader<T, D, STAGED>& map, const int (&pix)[4],
-                                                       const float2 (&w2)[4], int li,
-                                                       const uint4 (&qv)[RowCfg<T, D>::CH]) {
+__device__ __forceinline__ void corner_dots16(const MapReader<T, D, STAGED>& map, const int (&pix)[4], int li,
+                                              const uint4 (&qv)[RowCfg<T, D>::CH], float (&d)[4]) {
     using RC = RowCfg<T, D>;
     uint4 raw[4][RC::CH];
 #pragma unroll
     for (int c = 0; c < 4; ++c)
 #pragma unroll
         for (int ch = 0; ch < RC::CH; ++ch) raw[c][ch] = map.load(pix[c], ch * RC::G + li);
-    float d[4] = { 0.0f, 0.0f, 0.0f, 0.0f };
+#pragma unroll
+    for (int c = 0; c < 4; ++c) d[c] = 0.0f;
 #pragma unroll
     for (int ch = 0; ch < RC::CH; ++ch)
 #pragma unroll
         for (int c = 0; c < 4; ++c) d[c] = dot16<T>(qv[ch], raw[c][ch], d[c]);
+}
+
+// ... and this lane's part of sum_c w_c (qv . row_c): no interpolated row is ever formed.
+template <typename T, int D, bool STAGED>
+__device__ __forceinline__ float corner_weighted_dot16(const MapReader<T, D, STAGED>& map, const int (&pix)[4],
+                                                       const float2 (&w2)[4], int li,
+                                                       const uint4 (&qv)[RowCfg<T, D>::CH]) {
+    float d[4];
+    corner_dots16<T, D, STAGED>(map, pix, li, qv, d);
     return fmaf(w2[0].x, d[0], fmaf(w2[1].x, d[1], fmaf(w2[2].x, d[2], w2[3].x * d[3])));
 }
 
