@@ -349,3 +349,28 @@ def test_a_mirror_the_device_cannot_store_to_is_refused(backend):
         cabi.check(st)
     torch.cuda.synchronize()
     assert not out.any()
+
+
+@pytest.mark.parametrize("cfgname", ["C2", "C3", "C5"])
+def test_mirrors_at_benchmark_shapes(backend, cfgname):
+    """Same as above at the benchmark shapes (one batch element): staged and L1/L2 paths, gather
+    pass with and without split key pixels."""
+    from dataclasses import replace
+    cfg = replace(backend.inputs.CONFIGS[cfgname], B=1)
+    q, k, v, coords, dout = backend.inputs.make_inputs(cfg)
+    dev = torch.device("cuda", 0)
+    q, k, v, dout = (t.to(dev, cfg.dtype) for t in (q, k, v, dout))
+    coords = coords.to(dev)
+    args = (cfg.W, cfg.H, cfg.sm_scale)
+    out, lse = backend.forward_raw(q, k, v, coords, *args)
+    dq, dk, dv, _ = backend.backward_raw(q, k, v, coords, out, lse, dout, *args)
+    mir = {n: torch.zeros_like(q) for n in ("out", "dq", "dk", "dv")}
+    m_fwd = torch.zeros_like(q)
+    out2, lse2 = backend.forward_raw(q, k, v, coords, *args, out_mirror=m_fwd)
+    dq2, dk2, dv2, _ = backend.backward_raw(q, k, v, coords, out2, lse2, dout, *args, mirrors=mir)
+    torch.cuda.synchronize()
+    backend.cabi.check(backend.cabi.lib().dsdpa_device_error(0))
+    assert torch.equal(out, out2) and torch.equal(m_fwd, out) and torch.equal(mir["out"], out)
+    for name, a, b in (("dq", dq, dq2), ("dk", dk, dk2), ("dv", dv, dv2)):
+        assert torch.equal(a, b), name          # the two-pass backward is deterministic
+        assert torch.equal(mir[name], a), name
