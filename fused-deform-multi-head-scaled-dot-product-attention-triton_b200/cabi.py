@@ -33,6 +33,7 @@ FLAG_MAPS_FROM_L2 = 0x1
 FLAG_DETERMINISTIC = 0x2
 FLAG_SCATTER_GLOBAL = 0x4
 FLAG_SCATTER = 0x8
+FLAG_ROUNDED_WEIGHTS = 0x10
 
 # limit of dsdpa_backward_static_scratch (DSDPA_STATIC_SCRATCH_BYTES)
 STATIC_SCRATCH_BYTES = 64 << 20

@@ -33,7 +33,7 @@ int validate_problem(const dsdpa_problem* p) {
     if (p->D != 16 && p->D != 32 && p->D != 64 && p->D != 128 && p->D != 256) return DSDPA_ERR_BAD_HEAD_DIM;
     if (p->B <= 0 || p->V <= 0 || p->Hh <= 0 || p->W <= 0 || p->H <= 0 || p->S <= 0) return DSDPA_ERR_BAD_SHAPE;
     const unsigned known = DSDPA_FLAG_MAPS_FROM_L2 | DSDPA_FLAG_DETERMINISTIC | DSDPA_FLAG_SCATTER_GLOBAL |
-                           DSDPA_FLAG_SCATTER;
+                           DSDPA_FLAG_SCATTER | DSDPA_FLAG_ROUNDED_WEIGHTS;
     if (p->flags & ~known) return DSDPA_ERR_BAD_FLAGS;
     if ((p->flags & DSDPA_FLAG_DETERMINISTIC) && (p->flags & (DSDPA_FLAG_SCATTER | DSDPA_FLAG_SCATTER_GLOBAL)))
         return DSDPA_ERR_BAD_FLAGS;
@@ -64,6 +64,7 @@ TilePlan plan_tiles(const dsdpa_problem& p, bool backward, bool allow_priv) {
         return (long long)nstage * 2 * map_bytes + (priv ? 2 * acc_bytes : 0) + (long long)nw * kPlanRecBytesPerWarp + 16;
     };
     TilePlan best{};
+    best.rounded_weights = !backward && (p.flags & DSDPA_FLAG_ROUNDED_WEIGHTS) && p.dtype != DSDPA_F32;
     // mbarrier transaction counts hold 2^20-1 bytes; one stage is two maps
     const bool can_stage = !(p.flags & DSDPA_FLAG_MAPS_FROM_L2) && smem_need(1, 4, false) <= kPlanSmemMax &&
                            2 * map_bytes < (1ll << 20);
@@ -372,7 +373,8 @@ int dsdpa_describe_plan(const dsdpa_problem* p, char* text, size_t cap) {
     std::snprintf(text, cap,
                   "fwd[%s nstage=%d nw=%d nq=%d tiles=%d q_per_tile=%d ctas=%lld smem=%zu] "
                   "bwd_%s[%s%s nstage=%d nw=%d nq=%d tiles=%d q_per_tile=%d ctas=%lld smem=%zu]%s",
-                  f.staged ? "staged" : "l2", f.nstage, f.nw, f.nq, f.tiles, f.q_per_tile, f.ctas, f.smem,
+                  f.staged ? (f.rounded_weights ? "staged+rw" : "staged") : (f.rounded_weights ? "l2+rw" : "l2"), f.nstage,
+                  f.nw, f.nq, f.tiles, f.q_per_tile, f.ctas, f.smem,
                   two ? "pass_a" : "scatter", b.staged ? "staged" : "l2", b.priv ? "+priv" : "", b.nstage, b.nw, b.nq,
                   b.tiles, b.q_per_tile, b.ctas, b.smem, tail);
     return DSDPA_OK;

@@ -162,6 +162,32 @@ __device__ __forceinline__ float dot16(const uint4& a, const uint4& b, float acc
     return acc;
 }
 
+// Two fp32 scalars rounded to the 16-bit storage type (round to nearest even), returned as the
+// two 16-bit operands the mixed-precision fma takes.
+__device__ __forceinline__ void round_pair16(float a, float b, uint16_t& ra, uint16_t& rb, __nv_bfloat16*) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));   // upper half <- b, lower <- a
+    asm("mov.b32 {%0, %1}, %2;" : "=h"(ra), "=h"(rb) : "r"(r));
+}
+__device__ __forceinline__ void round_pair16(float a, float b, uint16_t& ra, uint16_t& rb, __half*) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+    asm("mov.b32 {%0, %1}, %2;" : "=h"(ra), "=h"(rb) : "r"(r));
+}
+// acc[0..3] += s * row for the eight 16-bit elements of `row` (pairs as unpack16_pairs orders them):
+// s is a 16-bit scalar, products are exact, the sums fp32.
+template <typename T>
+__device__ __forceinline__ void axpy16(uint16_t s, const uint4& row, float2* acc) {
+    const uint32_t w[4] = { row.x, row.y, row.z, row.w };
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint16_t lo, hi;
+        asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(w[i]));
+        acc[i].x = fma_mixed(s, lo, acc[i].x, (T*)nullptr);
+        acc[i].y = fma_mixed(s, hi, acc[i].y, (T*)nullptr);
+    }
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

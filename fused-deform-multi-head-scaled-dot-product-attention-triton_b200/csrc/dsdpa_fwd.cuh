@@ -218,8 +218,9 @@ __device__ __forceinline__ void corner_dots(const MapReader<T, D, STAGED>& map, 
     }
 }
 
-template <typename T, int D, int NQ, bool STAGED, int MAXT, int MINB>
+template <typename T, int D, int NQ, bool STAGED, int MAXT, int MINB, bool RW = false>
 __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
+    static_assert(!RW || sizeof(T) == 2, "rounded weights are a 16-bit storage option");
     using RC = RowCfg<T, D>;
     constexpr int G = RC::G, NG = RC::NG, EPL = RC::EPL, CH = RC::CH, EPV = RC::EPV, ROWB = RC::ROWB;
     constexpr int HP = EPL / 2;  // fp32 pairs per lane
@@ -383,13 +384,32 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
                         }
 #pragma unroll
                         for (int u = 0; u < U; ++u) {
-                            float2 vt[HP];
-                            gather_interp<T, D, STAGED>(vmap, pix[u], w2[u], li, vt);
                             const float pe = fast_exp2(sc[u] - m);
                             lsum += pe;
-                            const float2 p2 = make_float2(pe, pe);
+                            if constexpr (RW) {
+                                // (option) acc += sum_c (p*w_c) V_c straight from the stored rows: the
+                                // four weights p*w_c are rounded to the storage type (as the probabilities
+                                // are before the P.V product of a dense 16-bit attention kernel), products
+                                // exact, sums fp32; the normaliser keeps the unrounded p
+                                uint16_t s4[4];
+                                round_pair16(pe * w2[u][0].x, pe * w2[u][1].x, s4[0], s4[1], (T*)nullptr);
+                                round_pair16(pe * w2[u][2].x, pe * w2[u][3].x, s4[2], s4[3], (T*)nullptr);
+                                uint4 raw[4][CH];
 #pragma unroll
-                            for (int e = 0; e < HP; ++e) acc[j][e] = __ffma2_rn(p2, vt[e], acc[j][e]);
+                                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                                    for (int ch = 0; ch < CH; ++ch) raw[c][ch] = vmap.load(pix[u][c], ch * G + li);
+#pragma unroll
+                                for (int ch = 0; ch < CH; ++ch)
+#pragma unroll
+                                    for (int c = 0; c < 4; ++c) axpy16<T>(s4[c], raw[c][ch], &acc[j][ch * (EPV / 2)]);
+                            } else {
+                                float2 vt[HP];
+                                gather_interp<T, D, STAGED>(vmap, pix[u], w2[u], li, vt);
+                                const float2 p2 = make_float2(pe, pe);
+#pragma unroll
+                                for (int e = 0; e < HP; ++e) acc[j][e] = __ffma2_rn(p2, vt[e], acc[j][e]);
+                            }
                         }
                     }
                     __syncwarp();

@@ -46,9 +46,9 @@ inline cudaError_t allow_big_smem(K kern, bool (&done)[64]) {
     return e;
 }
 
-template <typename T, int D, int NQ, bool STAGED, int MAXT = (STAGED ? kStagedMaxThreads : kL2MaxThreads)>
+template <typename T, int D, int NQ, bool STAGED, bool RW = false, int MAXT = (STAGED ? kStagedMaxThreads : kL2MaxThreads)>
 inline cudaError_t fwd_one(const FwdParams& p, const TilePlan& plan, cudaStream_t stream) {
-    auto kern = fwd_kernel<T, D, NQ, STAGED, MAXT, STAGED ? 1 : kL2MinBlocks>;
+    auto kern = fwd_kernel<T, D, NQ, STAGED, MAXT, STAGED ? 1 : kL2MinBlocks, RW>;
     if (plan.nw * 32 > MAXT) return cudaErrorInvalidValue;
     static bool done[64] = {};  // a benign race at worst repeats the attribute call
     cudaError_t e = allow_big_smem(kern, done);
@@ -59,6 +59,16 @@ inline cudaError_t fwd_one(const FwdParams& p, const TilePlan& plan, cudaStream_
 
 template <typename T, int D>
 inline cudaError_t fwd_d(const FwdParams& p, const TilePlan& plan, cudaStream_t stream) {
+    if constexpr (sizeof(T) == 2) {
+        if (plan.rounded_weights) {
+            if (!plan.staged) return fwd_one<T, D, 1, false, true>(p, plan, stream);
+            switch (plan.nq) {
+                case 1: return fwd_one<T, D, 1, true, true>(p, plan, stream);
+                case 2: return fwd_one<T, D, 2, true, true>(p, plan, stream);
+                default: return cudaErrorInvalidValue;
+            }
+        }
+    }
     if (!plan.staged) return fwd_one<T, D, 1, false>(p, plan, stream);
     switch (plan.nq) {
         case 1: return fwd_one<T, D, 1, true>(p, plan, stream);

@@ -31,6 +31,7 @@ inline RowGeom row_geom(int D, int dtype) {
 struct TilePlan {
     bool staged;       // K/V maps of one key view staged in shared memory
     bool priv;         // backward only: dK/dV maps privatised in shared memory
+    bool rounded_weights;  // forward, 16-bit storage: DSDPA_FLAG_ROUNDED_WEIGHTS
     int nstage;        // map buffers (staged)
     int nw;            // warps per CTA
     int nq;            // query slots per group (template parameter)

@@ -61,6 +61,12 @@ typedef enum dsdpa_dtype {
 #define DSDPA_FLAG_SCATTER_GLOBAL  0x4u /* backward scatter: reductions straight to global memory,
                                            no shared-memory privatised accumulation */
 #define DSDPA_FLAG_SCATTER         0x8u /* backward: force the one-kernel scatter form */
+#define DSDPA_FLAG_ROUNDED_WEIGHTS 0x10u /* forward, 16-bit storage only (no effect on fp32): the weights
+                                           p*w_c that multiply the V rows are rounded to the storage type
+                                           first -- what casting P to bf16 before P.V is in dense attention
+                                           kernels -- so that V rows are never unpacked to fp32.  Products
+                                           stay exact and sums fp32; the reference keeps these weights in
+                                           fp32 (ops/triton.py:178), and so does the default */
 
 /* Problem description shared by all entry points. */
 typedef struct dsdpa_problem {

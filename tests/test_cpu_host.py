@@ -78,7 +78,7 @@ def test_null_and_misaligned_pointers():
 
 
 def test_status_strings_and_exceptions():
-    for st in range(0, 11):
+    for st in range(0, 12):
         assert cabi.status_string(st)
     assert cabi.status_string(12345) == "unknown status"
     with pytest.raises(NotImplementedError):
@@ -116,6 +116,19 @@ def test_plans_of_the_five_configurations():
     c1 = be.inputs.CONFIGS["C1"]
     text = cabi.describe_plan(cabi.Problem(c1.B, c1.V, c1.Hh, c1.W, c1.H, c1.D, c1.S, 0.5, cabi.F32, cabi.FLAG_MAPS_FROM_L2))
     assert text.startswith("fwd[l2")
+
+
+def test_rounded_weights_flag_is_a_16_bit_forward_option():
+    c5 = be.inputs.CONFIGS["C5"]
+    args = (c5.B, c5.V, c5.Hh, c5.W, c5.H, c5.D, c5.S, c5.sm_scale)
+    text = cabi.describe_plan(cabi.Problem(*args, cabi.BF16, cabi.FLAG_ROUNDED_WEIGHTS))
+    assert text.startswith("fwd[staged+rw")
+    text = cabi.describe_plan(cabi.Problem(*args, cabi.BF16, cabi.FLAG_ROUNDED_WEIGHTS | cabi.FLAG_MAPS_FROM_L2))
+    assert text.startswith("fwd[l2+rw")
+    c1 = be.inputs.CONFIGS["C1"]
+    text = cabi.describe_plan(cabi.Problem(c1.B, c1.V, c1.Hh, c1.W, c1.H, c1.D, c1.S, 0.5, cabi.F32,
+                                           cabi.FLAG_ROUNDED_WEIGHTS))
+    assert text.startswith("fwd[staged ")      # accepted, without effect on fp32 storage
 
 
 def test_operator_refuses_cpu_tensors():

@@ -374,3 +374,29 @@ def test_mirrors_at_benchmark_shapes(backend, cfgname):
     for name, a, b in (("dq", dq, dq2), ("dk", dk, dk2), ("dv", dv, dv2)):
         assert torch.equal(a, b), name          # the two-pass backward is deterministic
         assert torch.equal(mir[name], a), name
+
+
+@pytest.mark.parametrize("name", ["bf16_d64_uniform", "bf16_d64_clustered", "bf16_d32_oob", "d16_f16", "oob_f32"])
+@pytest.mark.parametrize("maps", ["staged", "l2"])
+def test_rounded_weights_option(backend, oracle, name, maps):
+    """DSDPA_FLAG_ROUNDED_WEIGHTS (16-bit storage, forward): the weights that multiply V rows are
+    rounded to the storage type.  Still within the storage type's tolerance of the reference and
+    of exact arithmetic on the stored inputs; no effect at all on fp32 storage."""
+    c = load_golden(name)
+    dt = c["dtype"]
+    dev = torch.device("cuda", 0)
+    q, k, v = (c[n].to(dev, dt) for n in ("q", "k", "v"))
+    coords = c["coords"].to(dev)
+    args = (c["W"], c["H"], c["sm_scale"])
+    base = 0x1 if maps == "l2" else 0
+    out0, lse0 = backend.forward_raw(q, k, v, coords, *args, flags=base)
+    out1, lse1 = backend.forward_raw(q, k, v, coords, *args, flags=base | backend.cabi.FLAG_ROUNDED_WEIGHTS)
+    torch.cuda.synchronize()
+    assert torch.equal(lse0, lse1)                      # the logits and the normaliser are untouched
+    if dt == torch.float32:
+        assert torch.equal(out0, out1)
+        return
+    exact, _ = oracle.forward(q.float().cpu(), k.float().cpu(), v.float().cpu(), c["coords"], *args)
+    assert rel_err(out1, c["out"]) < TOL[dt]
+    assert rel_err(out1, exact) < TOL[dt] / 2
+    assert rel_err(out0, exact) <= rel_err(out1, exact) * 1.5 + 1e-6   # the default is the more exact one
