@@ -50,6 +50,9 @@ def parse_args():
     ap.add_argument("--sweep", action="store_true",
                     help="the reference's own sweep instead of the benchmark line: views x samples in {2..12}, "
                          "forward and backward latency and peak memory (reference benchmark.py:16-57)")
+    ap.add_argument("--probes", action="store_true",
+                    help="measure the roofline denominators only: L2 read, shared-memory access patterns, "
+                         "L1-hit row gather; one JSON line")
     ap.add_argument("--profile-case", default=None, metavar="CFG:B:MODE[:FLAGS]",
                     help="run a small case of a configuration (e.g. C5:2:bwd) twice through the C ABI and exit: "
                          "the command the committed ncu captures were taken with")
@@ -235,6 +238,31 @@ def run_sweep():
                                   "peak_extra_MB": peak / 1e6}), flush=True)
 
 
+def measure_peaks(dev_index):
+    """Roofline denominators measured on this device by libdsdpa_probes.so (GB/s)."""
+    import torch
+    import ops
+    pr = ops.backend.probes
+    dev = torch.device("cuda", dev_index)
+    buf = torch.empty(32 << 20, dtype=torch.uint8, device=dev)
+    small = torch.zeros(64 << 10, dtype=torch.uint8, device=dev)
+    torch.cuda.synchronize(dev)
+    peaks = {"l2_read": pr.l2_read(buf.data_ptr(), buf.numel(), dev_index),
+             "l1_row_gather": pr.l1_row_gather(small.data_ptr(), dev_index),
+             "shared": {k: pr.shared_pattern(k, dev_index) for k in pr.SHARED_PATTERNS}}
+    torch.cuda.set_device(dev)
+    return peaks
+
+
+def run_probes():
+    import ops
+    pr = ops.backend.probes
+    peaks = measure_peaks(0)
+    print(json.dumps({"probes": {"l2_read_GBps": peaks["l2_read"], "l1_row_gather_GBps": peaks["l1_row_gather"],
+                                 "shared_GBps": {pr.SHARED_PATTERNS[k]: v for k, v in peaks["shared"].items()}}}),
+          flush=True)
+
+
 def run_profile_case(spec):
     """Forward (and backward) of configuration CFG with batch B, twice, for ncu to capture.
     MODE is fwd or bwd (= forward + backward); FLAGS are DSDPA_FLAG_* bits."""
@@ -273,6 +301,9 @@ def main():
         return
     if args.profile_case:
         run_profile_case(args.profile_case)
+        return
+    if args.probes:
+        run_probes()
         return
 
     import torch
@@ -551,15 +582,8 @@ def main():
             hbm_src = "measured"
         except (KeyError, ValueError):
             pass
-    g = ctypes.c_double()
-    buf = torch.empty(32 << 20, dtype=torch.uint8, device=dev)
-    cabi.check(lib.dsdpa_probe_l2_read_bandwidth(ctypes.c_void_p(buf.data_ptr()), buf.numel(), 5, local_rank, None,
-                                                 ctypes.byref(g)))
-    l2_peak = g.value
-    cabi.check(lib.dsdpa_probe_shared_read_bandwidth(5, local_rank, None, ctypes.byref(g)))
-    smem_peak = g.value
-    cabi.check(lib.dsdpa_probe_shared_row_gather_bandwidth(5, local_rank, None, ctypes.byref(g)))
-    smem_rows_peak = g.value
+    peaks = measure_peaks(local_rank)
+    l2_peak, smem_peak, smem_rows_peak = peaks["l2_read"], peaks["shared"][0], peaks["shared"][1]
     qh_rank = nb * cfg.V * nh * cfg.L
     gather_b = qh_rank * cfg.gather_bytes_per_qh()
     hbm_f = qh_rank * cfg.hbm_bytes_per_qh(False)

@@ -8,6 +8,7 @@ reference's name, positional signature and autograd contract
 from . import cabi  # noqa: F401
 from . import inputs  # noqa: F401
 from . import partition  # noqa: F401
+from . import probes  # noqa: F401  (measurement tooling; loads its library on first use only)
 from .host import HostPipeline  # noqa: F401
 from .op import deform_sdpa, deform_sdpa_triton, forward_raw, backward_raw  # noqa: F401
 

@@ -1,10 +1,12 @@
-"""Builds libdeform_sdpa.so (the C-ABI library) in-tree with nvcc for sm_100a.
+"""Builds the shared libraries in-tree with nvcc for sm_100a.
 
     python build.py [--force] [--jobs N]
 
 Every translation unit under csrc/ is compiled to csrc/_build/*.o in parallel and the
-objects are linked into libdeform_sdpa.so beside this file.  Nothing is installed
-outside the source tree.
+objects are linked into libdeform_sdpa.so (the C-ABI library, the product) beside this
+file; csrc/probes/*.cu become libdsdpa_probes.so, the bandwidth probes the benchmark uses
+for its roofline denominators (not linked into, or needed by, the product library).
+Nothing is installed outside the source tree.
 """
 from __future__ import annotations
 
@@ -19,6 +21,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OBJ = CSRC / "_build"
 LIB = HERE / "libdeform_sdpa.so"
+PROBES_LIB = HERE / "libdsdpa_probes.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -43,6 +46,7 @@ def _newest_header() -> float:
 
 def _compile(src: Path, force: bool, hdr_time: float) -> Path:
     obj = OBJ / (src.stem + ".o")
+    # -DNAME=value pairs for experiments and for the checked debug build
     if not force and obj.exists() and obj.stat().st_mtime >= max(src.stat().st_mtime, hdr_time):
         return obj
     extra = os.environ.get("DSDPA_NVCC_EXTRA", "").split()   # e.g. -DDSDPA_FWD_UNROLL=4, for experiments
@@ -54,18 +58,24 @@ def _compile(src: Path, force: bool, hdr_time: float) -> Path:
     return obj
 
 
-def build(force: bool = False, jobs: int | None = None) -> Path:
-    OBJ.mkdir(parents=True, exist_ok=True)
-    srcs = sorted(CSRC.glob("*.cu"))
-    hdr_time = _newest_header()
-    jobs = jobs or min(len(srcs), os.cpu_count() or 4)
-    with ThreadPoolExecutor(max_workers=jobs) as pool:
-        objs = list(pool.map(lambda s: _compile(s, force, hdr_time), srcs))
-    if force or not LIB.exists() or LIB.stat().st_mtime < max(o.stat().st_mtime for o in objs):
-        cmd = [_nvcc(), "-shared", "-o", str(LIB), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"]
+def _link(lib: Path, objs: list[Path], force: bool) -> None:
+    if force or not lib.exists() or lib.stat().st_mtime < max(o.stat().st_mtime for o in objs):
+        cmd = [_nvcc(), "-shared", "-o", str(lib), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+
+
+def build(force: bool = False, jobs: int | None = None) -> Path:
+    OBJ.mkdir(parents=True, exist_ok=True)
+    srcs = sorted(CSRC.glob("*.cu"))
+    probe_srcs = sorted((CSRC / "probes").glob("*.cu"))
+    hdr_time = _newest_header()
+    jobs = jobs or min(len(srcs) + len(probe_srcs), os.cpu_count() or 4)
+    with ThreadPoolExecutor(max_workers=jobs) as pool:
+        objs = list(pool.map(lambda s: _compile(s, force, hdr_time), srcs + probe_srcs))
+    _link(LIB, objs[:len(srcs)], force)
+    _link(PROBES_LIB, objs[len(srcs):], force)
     return LIB
 
 

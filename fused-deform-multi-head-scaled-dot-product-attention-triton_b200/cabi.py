@@ -58,9 +58,6 @@ EXPORTS = (
     "dsdpa_kernel_launches",
     "dsdpa_device_error",
     "dsdpa_describe_plan",
-    "dsdpa_probe_l2_read_bandwidth",
-    "dsdpa_probe_shared_read_bandwidth",
-    "dsdpa_probe_shared_row_gather_bandwidth",
 )
 
 
@@ -129,12 +126,6 @@ def lib() -> ctypes.CDLL:
     L.dsdpa_device_error.restype = ci
     L.dsdpa_describe_plan.argtypes = [pp, ctypes.c_char_p, ctypes.c_size_t]
     L.dsdpa_describe_plan.restype = ci
-    L.dsdpa_probe_l2_read_bandwidth.argtypes = [vp, ctypes.c_size_t, ci, ci, vp, ctypes.POINTER(ctypes.c_double)]
-    L.dsdpa_probe_l2_read_bandwidth.restype = ci
-    L.dsdpa_probe_shared_read_bandwidth.argtypes = [ci, ci, vp, ctypes.POINTER(ctypes.c_double)]
-    L.dsdpa_probe_shared_read_bandwidth.restype = ci
-    L.dsdpa_probe_shared_row_gather_bandwidth.argtypes = [ci, ci, vp, ctypes.POINTER(ctypes.c_double)]
-    L.dsdpa_probe_shared_row_gather_bandwidth.restype = ci
     _lib = L
     return L
 

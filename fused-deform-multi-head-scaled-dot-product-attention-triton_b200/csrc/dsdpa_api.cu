@@ -21,10 +21,24 @@ static int cuda_fail(cudaError_t e) {
     return DSDPA_ERR_CUDA;
 }
 
-int env_int(const char* name, int fallback) {
+// Sweep knobs (environment variables DSDPA_*), read once per process: the planner runs on every
+// call and must not walk the environment there.
+struct Knobs {
+    int fwd_nw, fwd_nq, bwd_nw, bwd_nq;
+    int gather_smem_kb, index_smem_kb, gather_qb, gather_threads, gather_nslab, bwd_two_pass;
+};
+static int env_int(const char* name, int fallback) {
     const char* s = std::getenv(name);
     if (!s || !*s) return fallback;
     return std::atoi(s);
+}
+static const Knobs& knobs() {
+    static const Knobs k = {
+        env_int("DSDPA_FWD_NW", 0), env_int("DSDPA_FWD_NQ", 0), env_int("DSDPA_BWD_NW", 0), env_int("DSDPA_BWD_NQ", 0),
+        env_int("DSDPA_GATHER_SMEM_KB", 224), env_int("DSDPA_INDEX_SMEM_KB", 112), env_int("DSDPA_GATHER_QB", 0),
+        env_int("DSDPA_GATHER_THREADS", 768), env_int("DSDPA_GATHER_NSLAB", 0), env_int("DSDPA_BWD_TWO_PASS", 1),
+    };
+    return k;
 }
 
 int validate_problem(const dsdpa_problem* p) {
@@ -53,12 +67,8 @@ TilePlan plan_tiles(const dsdpa_problem& p, bool backward, bool allow_priv) {
     const long long acc_bytes = (long long)L * p.D * 4;
     const RowGeom rg = row_geom(p.D, p.dtype);
     const int ch = (p.D * dtype_size(p.dtype) / 16) / rg.G;
-    const char* pre = backward ? "DSDPA_BWD" : "DSDPA_FWD";
-    char name[64];
-    std::snprintf(name, sizeof name, "%s_NW", pre);
-    const int force_nw = env_int(name, 0);
-    std::snprintf(name, sizeof name, "%s_NQ", pre);
-    const int force_nq = env_int(name, 0);
+    const int force_nw = backward ? knobs().bwd_nw : knobs().fwd_nw;
+    const int force_nq = backward ? knobs().bwd_nq : knobs().fwd_nq;
 
     auto smem_need = [&](int nstage, int nw, bool priv) -> long long {
         return (long long)nstage * 2 * map_bytes + (priv ? 2 * acc_bytes : 0) + (long long)nw * kPlanRecBytesPerWarp + 16;
@@ -137,7 +147,7 @@ GatherPlan plan_gather(const dsdpa_problem& p) {
     const int L = p.W * p.H;
     const long long rowb = (long long)p.D * dtype_size(p.dtype);
     const long long per_query = 2 * rowb + (long long)p.S * 8;
-    const long long budget = (long long)env_int("DSDPA_GATHER_SMEM_KB", 224) * 1024;
+    const long long budget = (long long)knobs().gather_smem_kb * 1024;
     long long qb_max = ((budget < kPlanSmemMax ? budget : kPlanSmemMax) - 64) / per_query;
     qb_max &= ~1ll;  // even, so that every tile's scalars start on a 16-byte boundary
     // entries address a query's row in 16-byte units and a sample's scalars by index, 16 bits each
@@ -147,18 +157,18 @@ GatherPlan plan_gather(const dsdpa_problem& p) {
         // The index builder scatters 8-byte entries; with many CTAs per SM their half-written
         // 32-byte sectors outgrow L2 and are evicted before they are complete.  Asking for more
         // shared memory than needed caps the CTAs per SM at two (measured best).
-        const size_t floor_kb = (size_t)env_int("DSDPA_INDEX_SMEM_KB", 112);
+        const size_t floor_kb = (size_t)knobs().index_smem_kb;
         if (floor_kb * 1024 > index_smem && floor_kb * 1024 <= (size_t)kPlanSmemMax) index_smem = floor_kb * 1024;
     }
     if (qb_max < 2 || p.S > 65535 || index_smem > (size_t)kPlanSmemMax) return g;  // ok = false
-    const int force_qb = env_int("DSDPA_GATHER_QB", 0);
+    const int force_qb = knobs().gather_qb;
     if (force_qb >= 2 && force_qb <= qb_max) qb_max = force_qb & ~1;
     g.tpv = (int)((L + qb_max - 1) / qb_max);
     int qb = (L + g.tpv - 1) / g.tpv;
     qb += qb & 1;
     g.QB = qb;
     g.ok = true;
-    g.gather_threads = env_int("DSDPA_GATHER_THREADS", 768);
+    g.gather_threads = knobs().gather_threads;
     if (g.gather_threads < 32 || g.gather_threads > 768 || g.gather_threads % 32) g.gather_threads = 768;
     g.gather_smem = (size_t)qb * 2 * rowb + (((size_t)qb * p.S * 8 + 15) & ~(size_t)15) + 16;
     // One CTA per SM: when the grid is only a few waves long and the last one is poorly filled,
@@ -174,7 +184,7 @@ GatherPlan plan_gather(const dsdpa_problem& p) {
             const double eff = (double)ctas / (double)(waves * kPlanSMs) * (1.0 - 0.02 * (ns - 1));
             if (eff > best_eff + 1e-9) { best_eff = eff; best = ns; }
         }
-        const int force = env_int("DSDPA_GATHER_NSLAB", 0);
+        const int force = knobs().gather_nslab;
         g.nslab = force >= 1 && force <= 8 ? force : best;
         g.gather_ctas = units * g.nslab;
     }
@@ -193,7 +203,7 @@ static bool use_two_pass(const dsdpa_problem& p, const GatherPlan& g) {
     if (!g.ok) return false;
     if (p.flags & (DSDPA_FLAG_SCATTER | DSDPA_FLAG_SCATTER_GLOBAL)) return false;
     if (p.flags & DSDPA_FLAG_DETERMINISTIC) return true;
-    return env_int("DSDPA_BWD_TWO_PASS", 1) != 0;
+    return knobs().bwd_two_pass != 0;
 }
 
 static bool misaligned(const void* p) { return ((uintptr_t)p & 15u) != 0; }
@@ -264,69 +274,6 @@ static cudaError_t launch_copy16(const void* src, void* dst, size_t bytes, cudaS
     const unsigned grid = (unsigned)(want < (size_t)kPlanSMs * 4 ? want : (size_t)kPlanSMs * 4);
     copy16_kernel<<<grid, 512, 0, s>>>((const uint4*)src, (uint4*)dst, n16);
     return cudaGetLastError();
-}
-
-// ---- bandwidth probes -------------------------------------------------------------
-__device__ unsigned g_probe_sink;  // never read; keeps the probes' loads alive
-
-__global__ void __launch_bounds__(1024, 1) probe_l2_kernel(const uint4* __restrict__ buf, size_t nvec) {
-    // every CTA sweeps the whole buffer, starting at its own offset
-    const size_t start = (size_t)blockIdx.x * 4099u * 1024u % nvec;
-    unsigned acc = 0;
-    const size_t stride = blockDim.x;
-    size_t i = threadIdx.x;
-    for (; i + 3 * stride < nvec; i += 4 * stride) {
-        size_t a = start + i; if (a >= nvec) a -= nvec;
-        size_t b = start + i + stride; if (b >= nvec) b -= nvec;
-        size_t c = start + i + 2 * stride; if (c >= nvec) c -= nvec;
-        size_t d = start + i + 3 * stride; if (d >= nvec) d -= nvec;
-        const uint4 x0 = ldg128_stream(buf + a), x1 = ldg128_stream(buf + b);
-        const uint4 x2 = ldg128_stream(buf + c), x3 = ldg128_stream(buf + d);
-        acc ^= x0.x ^ x0.w ^ x1.y ^ x1.z ^ x2.x ^ x2.w ^ x3.y ^ x3.z;
-    }
-    if (acc == 0x9e3779b9u) g_probe_sink = acc;
-}
-
-__global__ void __launch_bounds__(1024, 1) probe_smem_kernel(int rounds) {
-    extern __shared__ __align__(128) unsigned char smem[];
-    const uint32_t base = smem_addr(smem);
-    // 64 KB window, every lane reads its own 16 bytes of a 512-byte warp line: conflict-free
-    for (uint32_t o = threadIdx.x * 16u; o < 65536u; o += blockDim.x * 16u) sts128(base + o, make_uint4(o, o + 1, o + 2, o + 3));
-    __syncthreads();
-    unsigned acc = 0;
-    uint32_t off = threadIdx.x * 16u;
-    for (int r = 0; r < rounds; ++r) {
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const uint4 x = lds128(base + ((off + u * 16384u) & 65535u));
-            acc ^= x.x ^ x.y ^ x.z ^ x.w;
-        }
-        off = (off + 512u * 7u) & 65535u;
-    }
-    if (acc == 0x9e3779b9u) g_probe_sink = acc;
-}
-
-// The access pattern of the kernels' gathers: every group of eight lanes reads one 128-byte
-// row at a pseudo-random row index of a 64 KB window (row-aligned, so each group is
-// conflict-free by itself; different groups of a warp hit unrelated rows).
-__global__ void __launch_bounds__(1024, 1) probe_smem_rows_kernel(int rounds) {
-    extern __shared__ __align__(128) unsigned char smem[];
-    const uint32_t base = smem_addr(smem);
-    for (uint32_t o = threadIdx.x * 16u; o < 65536u; o += blockDim.x * 16u) sts128(base + o, make_uint4(o, o + 1, o + 2, o + 3));
-    __syncthreads();
-    unsigned acc = 0;
-    const uint32_t li = threadIdx.x & 7u;
-    uint32_t state = (threadIdx.x >> 3) * 2654435761u + 12345u;   // one generator per group
-    for (int r = 0; r < rounds; ++r) {
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            state = state * 1664525u + 1013904223u;
-            const uint32_t row = (state >> 13) & 511u;             // 512 rows of 128 bytes
-            const uint4 x = lds128(base + row * 128u + li * 16u);
-            acc ^= x.x ^ x.y ^ x.z ^ x.w;
-        }
-    }
-    if (acc == 0x9e3779b9u) g_probe_sink = acc;
 }
 
 }  // namespace dsdpa
@@ -623,76 +570,6 @@ int dsdpa_device_error(int device) {
     word = 0;
     if ((e = cudaMemcpyToSymbol(g_error_word, &word, sizeof(int))) != cudaSuccess) return cuda_fail(e);
     return DSDPA_ERR_DEVICE_TIMEOUT;
-}
-
-static int time_probe(cudaStream_t s, int iters, double bytes_per_iter, double* gbps, void (*launch)(cudaStream_t, void*),
-                      void* ctx) {
-    cudaEvent_t a, b;
-    cudaError_t e;
-    if ((e = cudaEventCreate(&a)) != cudaSuccess) return cuda_fail(e);
-    if ((e = cudaEventCreate(&b)) != cudaSuccess) { cudaEventDestroy(a); return cuda_fail(e); }
-    launch(s, ctx);  // warm-up
-    cudaEventRecord(a, s);
-    for (int i = 0; i < iters; ++i) launch(s, ctx);
-    cudaEventRecord(b, s);
-    e = cudaEventSynchronize(b);
-    float ms = 0.0f;
-    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, a, b);
-    cudaEventDestroy(a);
-    cudaEventDestroy(b);
-    if (e == cudaSuccess) e = cudaGetLastError();
-    if (e != cudaSuccess) return cuda_fail(e);
-    *gbps = bytes_per_iter * iters / ((double)ms * 1e-3) / 1e9;
-    return DSDPA_OK;
-}
-
-struct L2Ctx { const uint4* buf; size_t nvec; int ctas; };
-static void launch_l2(cudaStream_t s, void* c) {
-    L2Ctx* x = (L2Ctx*)c;
-    probe_l2_kernel<<<x->ctas, 1024, 0, s>>>(x->buf, x->nvec);
-}
-struct SmemCtx { int rounds; int ctas; };
-static void launch_smem(cudaStream_t s, void* c) {
-    SmemCtx* x = (SmemCtx*)c;
-    probe_smem_kernel<<<x->ctas, 1024, 65536, s>>>(x->rounds);
-}
-
-int dsdpa_probe_l2_read_bandwidth(const void* buffer, size_t bytes, int iters, int device, void* stream, double* gbps) {
-    if (!buffer || !gbps) return DSDPA_ERR_NULL_POINTER;
-    if (misaligned(buffer)) return DSDPA_ERR_MISALIGNED;
-    if (bytes < (1u << 20) || iters <= 0) return DSDPA_ERR_BAD_SHAPE;
-    DeviceGuard guard(device);
-    if (guard.err != cudaSuccess) return cuda_fail(guard.err);
-    L2Ctx c{ (const uint4*)buffer, bytes / 16 / 4096 * 4096, kSMs };
-    return time_probe((cudaStream_t)stream, iters, (double)c.nvec * 16.0 * c.ctas, gbps, launch_l2, &c);
-}
-
-static void launch_smem_rows(cudaStream_t s, void* c) {
-    SmemCtx* x = (SmemCtx*)c;
-    probe_smem_rows_kernel<<<x->ctas, 1024, 65536, s>>>(x->rounds);
-}
-
-int dsdpa_probe_shared_row_gather_bandwidth(int iters, int device, void* stream, double* gbps) {
-    if (!gbps) return DSDPA_ERR_NULL_POINTER;
-    if (iters <= 0) return DSDPA_ERR_BAD_SHAPE;
-    DeviceGuard guard(device);
-    if (guard.err != cudaSuccess) return cuda_fail(guard.err);
-    cudaError_t e = cudaFuncSetAttribute(probe_smem_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
-    if (e != cudaSuccess) return cuda_fail(e);
-    SmemCtx c{ 4096, kSMs };
-    return time_probe((cudaStream_t)stream, iters, (double)c.rounds * 8.0 * 16.0 * 1024.0 * c.ctas, gbps, launch_smem_rows,
-                      &c);
-}
-
-int dsdpa_probe_shared_read_bandwidth(int iters, int device, void* stream, double* gbps) {
-    if (!gbps) return DSDPA_ERR_NULL_POINTER;
-    if (iters <= 0) return DSDPA_ERR_BAD_SHAPE;
-    DeviceGuard guard(device);
-    if (guard.err != cudaSuccess) return cuda_fail(guard.err);
-    cudaError_t e = cudaFuncSetAttribute(probe_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
-    if (e != cudaSuccess) return cuda_fail(e);
-    SmemCtx c{ 4096, kSMs };
-    return time_probe((cudaStream_t)stream, iters, (double)c.rounds * 8.0 * 16.0 * 1024.0 * c.ctas, gbps, launch_smem, &c);
 }
 
 }  // extern "C"

@@ -58,9 +58,6 @@ struct GatherPlan {
 };
 GatherPlan plan_gather(const dsdpa_problem& p);
 
-// Environment overrides for experiments: DSDPA_<which>_NW, DSDPA_<which>_NQ.
-int env_int(const char* name, int fallback);
-
 // `backward`: plan for the scatter kernel (it can additionally privatise dK/dV).
 TilePlan plan_tiles(const dsdpa_problem& p, bool backward, bool allow_priv);
 

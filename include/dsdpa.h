@@ -222,24 +222,6 @@ int dsdpa_device_error(int device);
  */
 int dsdpa_describe_plan(const dsdpa_problem* p, char* text, size_t cap);
 
-/*
- * Measurement helpers used by the benchmark to obtain roofline denominators on the
- * device at hand.  Each runs a read-only kernel on `stream` `iters` times after one
- * warm-up, times it with CUDA events on that stream, synchronises, and returns GB/s
- * in *gbps.
- *   l2:      every SM reads a `bytes`-sized buffer (<= L2 size, caller-provided) with
- *            128-bit read-only loads.
- *   shared:  every SM reads its own shared memory with conflict-free 128-bit loads, every
- *            warp a contiguous 512-byte line.
- *   shared row gather:  the kernels' own access pattern -- every group of eight lanes reads a
- *            128-byte row at an unrelated row index -- i.e. the ceiling a gather of whole
- *            rows from shared memory can reach.
- */
-int dsdpa_probe_l2_read_bandwidth(const void* buffer, size_t bytes, int iters,
-                                  int device, void* stream, double* gbps);
-int dsdpa_probe_shared_read_bandwidth(int iters, int device, void* stream, double* gbps);
-int dsdpa_probe_shared_row_gather_bandwidth(int iters, int device, void* stream, double* gbps);
-
 #ifdef __cplusplus
 }
 #endif
