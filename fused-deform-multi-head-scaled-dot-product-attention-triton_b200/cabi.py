@@ -45,6 +45,7 @@ PEER_HANDLE_BYTES = 64
 EXPORTS = (
     "dsdpa_forward",
     "dsdpa_backward_workspace_bytes",
+    "dsdpa_backward_supports_dcoords",
     "dsdpa_backward",
     "dsdpa_forward_mirrored",
     "dsdpa_backward_mirrored",
@@ -100,6 +101,8 @@ def lib() -> ctypes.CDLL:
     L.dsdpa_forward.restype = ci
     L.dsdpa_backward_workspace_bytes.argtypes = [pp]
     L.dsdpa_backward_workspace_bytes.restype = ctypes.c_size_t
+    L.dsdpa_backward_supports_dcoords.argtypes = [pp]
+    L.dsdpa_backward_supports_dcoords.restype = ci
     L.dsdpa_backward.argtypes = [pp] + [vp] * 11 + [vp, ctypes.c_size_t, ci, vp]
     L.dsdpa_backward.restype = ci
     L.dsdpa_forward_mirrored.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, ci, vp]

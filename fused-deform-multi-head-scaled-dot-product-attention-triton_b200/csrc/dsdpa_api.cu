@@ -145,22 +145,35 @@ TilePlan plan_tiles(const dsdpa_problem& p, bool backward, bool allow_priv) {
 GatherPlan plan_gather(const dsdpa_problem& p) {
     GatherPlan g{};
     const int L = p.W * p.H;
+    const long long A = (long long)p.H * (p.W + 1);   // anchors: pixel pairs (x-1, x) of one map row
     const long long rowb = (long long)p.D * dtype_size(p.dtype);
     const long long per_query = 2 * rowb + (long long)p.S * 8;
+    g.gather_threads = knobs().gather_threads;
+    if (g.gather_threads < 32 || g.gather_threads > kGatherMaxThreads || g.gather_threads % 32)
+        g.gather_threads = kGatherMaxThreads;
+    // every group of lanes keeps a small ring of index entries in shared memory
+    const RowGeom rg = row_geom(p.D, p.dtype);
+    const long long chunk = rg.G < 8 ? rg.G : 8;
+    const long long ring_bytes = (long long)(g.gather_threads / 32) * rg.NG * (2 * chunk * 16 + 16);
     const long long budget = (long long)knobs().gather_smem_kb * 1024;
-    long long qb_max = ((budget < kPlanSmemMax ? budget : kPlanSmemMax) - 64) / per_query;
+    long long qb_max = ((budget < kPlanSmemMax ? budget : kPlanSmemMax) - 64 - ring_bytes) / per_query;
     qb_max &= ~1ll;  // even, so that every tile's scalars start on a 16-byte boundary
-    // entries address a query's row in 16-byte units and a sample's scalars by index, 16 bits each
-    while (qb_max > 2 && (qb_max * rowb / 16 > 65535 || qb_max * p.S > 65535)) qb_max -= 2;
-    size_t index_smem = ((size_t)8 * L + 256) * sizeof(int);
+    // entries hold byte offsets into the tile's rows and scalars as 32-bit fields; one segment's
+    // entry count must stay an int
+    while (qb_max > 2 && qb_max * p.S * 2 > (1ll << 30)) qb_max -= 2;
+    // The index builder keeps one histogram over the anchors per sample-taking warp: eight when
+    // they fit, fewer for large maps (slower to build, same lists).
+    long long nhist = ((long long)kPlanSmemMax - 1024) / (A * 4);
+    if (nhist > 8) nhist = 8;
+    if (qb_max < 2 || nhist < 1 || A + 1 >= (1ll << 30)) return g;  // ok = false
+    size_t index_smem = ((size_t)nhist * A + 256) * sizeof(int);
     {
-        // The index builder scatters 8-byte entries; with many CTAs per SM their half-written
+        // The index builder scatters 16-byte entries; with many CTAs per SM their half-written
         // 32-byte sectors outgrow L2 and are evicted before they are complete.  Asking for more
         // shared memory than needed caps the CTAs per SM at two (measured best).
         const size_t floor_kb = (size_t)knobs().index_smem_kb;
         if (floor_kb * 1024 > index_smem && floor_kb * 1024 <= (size_t)kPlanSmemMax) index_smem = floor_kb * 1024;
     }
-    if (qb_max < 2 || p.S > 65535 || index_smem > (size_t)kPlanSmemMax) return g;  // ok = false
     const int force_qb = knobs().gather_qb;
     if (force_qb >= 2 && force_qb <= qb_max) qb_max = force_qb & ~1;
     g.tpv = (int)((L + qb_max - 1) / qb_max);
@@ -168,33 +181,36 @@ GatherPlan plan_gather(const dsdpa_problem& p) {
     qb += qb & 1;
     g.QB = qb;
     g.ok = true;
-    g.gather_threads = knobs().gather_threads;
-    if (g.gather_threads < 32 || g.gather_threads > 768 || g.gather_threads % 32) g.gather_threads = 768;
-    g.gather_smem = (size_t)qb * 2 * rowb + (((size_t)qb * p.S * 8 + 15) & ~(size_t)15) + 16;
+    g.A = (int)A;
+    g.nhist = (int)nhist;
+    g.gather_smem = (size_t)qb * 2 * rowb + (((size_t)qb * p.S * 8 + 15) & ~(size_t)15) + 16 + (size_t)ring_bytes;
     // One CTA per SM: when the grid is only a few waves long and the last one is poorly filled,
-    // split every unit's key pixels over 2-4 CTAs.
+    // split every unit's map rows over 2-4 CTAs.
     {
         const long long units = (long long)p.B * p.Hh * p.V;
         int best = 1;
         double best_eff = 0.0;
-        for (int ns = 1; ns <= 4; ++ns) {
+        for (int ns = 1; ns <= 4 && ns <= p.H; ++ns) {
             const long long ctas = units * ns;
             const long long waves = (ctas + kPlanSMs - 1) / kPlanSMs;
-            // every extra CTA of a unit reloads the tiles: charge 2% per split
-            const double eff = (double)ctas / (double)(waves * kPlanSMs) * (1.0 - 0.02 * (ns - 1));
+            // every extra CTA of a unit reloads the tiles (2% per split), and the slabs are whole
+            // map rows, so the largest slab sets the pace
+            const int rows = (p.H + ns - 1) / ns;
+            const double eff = (double)ctas / (double)(waves * kPlanSMs) * (1.0 - 0.02 * (ns - 1)) *
+                               ((double)p.H / ((double)rows * ns));
             if (eff > best_eff + 1e-9) { best_eff = eff; best = ns; }
         }
         const int force = knobs().gather_nslab;
-        g.nslab = force >= 1 && force <= 8 ? force : best;
+        g.nslab = force >= 1 && force <= 8 && force <= p.H ? force : best;
         g.gather_ctas = units * g.nslab;
     }
     const long long T = (long long)p.V * g.tpv;
     g.segments = (long long)p.B * T * p.V;
     g.index_smem = index_smem;
     g.scal_bytes = (((size_t)p.B * p.Hh * T * p.V * qb * p.S * 8) + 16 + 255) & ~(size_t)255;
-    g.seg_entries = (int)(((long long)qb * p.S * 4 + 3ll * L + 3) & ~3ll);
-    g.entries_bytes = (((size_t)g.segments * g.seg_entries * 8) + 255) & ~(size_t)255;
-    g.rowptr_bytes = (((size_t)g.segments * (L + 1) * 4) + 255) & ~(size_t)255;
+    g.seg_entries = (int)((long long)qb * p.S * 2);
+    g.entries_bytes = (((size_t)g.segments * g.seg_entries * 16) + 255) & ~(size_t)255;
+    g.rowptr_bytes = (((size_t)g.segments * (A + 1) * 4) + 255) & ~(size_t)255;
     return g;
 }
 
@@ -370,14 +386,27 @@ int dsdpa_forward_mirrored(const dsdpa_problem* p, const void* q, const void* k,
     return DSDPA_OK;
 }
 
+// fp32 dK/dV accumulators inside the workspace.  Scatter forms: one pair of maps for 16-bit
+// storage (fp32 storage accumulates in dk/dv).  Two-pass form: a "left" and a "right" pair;
+// for fp32 storage the left pair is dk/dv themselves.
+static size_t accumulator_bytes(const dsdpa_problem& p, bool two_pass) {
+    const size_t n = (size_t)p.B * p.V * p.Hh * p.W * p.H * p.D;
+    const size_t maps = (p.dtype == DSDPA_F32 ? 0 : 2) + (two_pass ? 2 : 0);
+    return maps == 0 ? 0 : ((maps * n * sizeof(float) + 255) & ~(size_t)255);
+}
+
 size_t dsdpa_backward_workspace_bytes(const dsdpa_problem* p) {
     if (validate_problem(p) != DSDPA_OK) return 0;
-    const size_t n = (size_t)p->B * p->V * p->Hh * p->W * p->H * p->D;
-    // fp32 storage accumulates dK/dV in the outputs themselves
-    size_t bytes = p->dtype == DSDPA_F32 ? 0 : ((2 * n * sizeof(float) + 255) & ~(size_t)255);
     const GatherPlan g = plan_gather(*p);
-    if (use_two_pass(*p, g)) bytes += g.scal_bytes + g.entries_bytes + g.rowptr_bytes;
+    const bool two = use_two_pass(*p, g);
+    size_t bytes = accumulator_bytes(*p, two);
+    if (two) bytes += g.scal_bytes + g.entries_bytes + g.rowptr_bytes;
     return bytes;
+}
+
+int dsdpa_backward_supports_dcoords(const dsdpa_problem* p) {
+    if (validate_problem(p) != DSDPA_OK) return 0;
+    return use_two_pass(*p, plan_gather(*p)) ? 1 : 0;
 }
 
 int dsdpa_backward(const dsdpa_problem* p, const void* q, const void* k, const void* v, const float* coords,
@@ -420,17 +449,23 @@ int dsdpa_backward_mirrored(const dsdpa_problem* p, const void* q, const void* k
         const size_t nc = (size_t)p->B * p->V * p->W * p->H * p->V * p->S * 2;
         if ((e = cudaMemsetAsync(dcoords, 0, nc * sizeof(float), s)) != cudaSuccess) return cuda_fail(e);
     }
-    const size_t acc_bytes = p->dtype == DSDPA_F32 ? 0 : ((2 * n * sizeof(float) + 255) & ~(size_t)255);
+    const size_t acc_bytes = accumulator_bytes(*p, two_pass);
     float* dk32 = p->dtype == DSDPA_F32 ? (float*)dk : (float*)workspace;
     float* dv32 = p->dtype == DSDPA_F32 ? (float*)dv : (float*)workspace + n;
-    if ((e = cudaMemsetAsync(dk32, 0, n * sizeof(float), s)) != cudaSuccess) return cuda_fail(e);
-    if ((e = cudaMemsetAsync(dv32, 0, n * sizeof(float), s)) != cudaSuccess) return cuda_fail(e);
+    // two-pass form: the second ("right") pair of maps lies behind the first in the workspace
+    float* dk_right = two_pass ? (float*)workspace + (p->dtype == DSDPA_F32 ? 0 : 2 * n) : nullptr;
+    float* dv_right = two_pass ? dk_right + n : nullptr;
+    if (p->dtype == DSDPA_F32) {
+        if ((e = cudaMemsetAsync(dk32, 0, n * sizeof(float), s)) != cudaSuccess) return cuda_fail(e);
+        if ((e = cudaMemsetAsync(dv32, 0, n * sizeof(float), s)) != cudaSuccess) return cuda_fail(e);
+    }
+    if (acc_bytes > 0 && (e = cudaMemsetAsync(workspace, 0, acc_bytes, s)) != cudaSuccess) return cuda_fail(e);
 
     const int L = p->W * p->H;
     const float hw = (float)(p->W - 1) * 0.5f, hh = (float)(p->H - 1) * 0.5f;
     char* ws = (char*)workspace + acc_bytes;
     float2* scal = two_pass ? (float2*)ws : nullptr;
-    uint2* entries = two_pass ? (uint2*)(ws + gp.scal_bytes) : nullptr;
+    uint4* entries = two_pass ? (uint4*)(ws + gp.scal_bytes) : nullptr;
     int* rowptr = two_pass ? (int*)(ws + gp.scal_bytes + gp.entries_bytes) : nullptr;
 
     if (two_pass) {
@@ -439,7 +474,8 @@ int dsdpa_backward_mirrored(const dsdpa_problem* p, const void* q, const void* k
         ip.coords = coords; ip.rowptr = rowptr; ip.entries = entries;
         ip.B = p->B; ip.V = p->V; ip.W = p->W; ip.H = p->H; ip.L = L; ip.S = p->S;
         ip.hw = hw; ip.hh = hh; ip.tpv = gp.tpv; ip.QB = gp.QB;
-        ip.rowb16 = p->D * dtype_size(p->dtype) / 16; ip.seg_entries = gp.seg_entries;
+        ip.rowb = p->D * dtype_size(p->dtype); ip.seg_entries = gp.seg_entries;
+        ip.A = gp.A; ip.nhist = gp.nhist;
         static bool index_attr[64] = {};
         if ((e = detail::allow_big_smem(index_build_kernel<kIndexWarpsDefault>, index_attr)) != cudaSuccess) return cuda_fail(e);
         index_build_kernel<kIndexWarpsDefault><<<(unsigned)gp.segments, kIndexWarpsDefault * 32, gp.index_smem, s>>>(ip);
@@ -476,10 +512,10 @@ int dsdpa_backward_mirrored(const dsdpa_problem* p, const void* q, const void* k
     if (two_pass) {
         GatherParams g{};
         g.q = q; g.dout = dout; g.scal = scal; g.rowptr = rowptr; g.entries = entries;
-        g.dk32 = dk32; g.dv32 = dv32;
+        g.dk_left = dk32; g.dv_left = dv32; g.dk_right = dk_right; g.dv_right = dv_right;
         g.dk = dk; g.dv = dv; g.dk_mirror = mir.dk; g.dv_mirror = mir.dv;
-        g.B = p->B; g.V = p->V; g.Hh = p->Hh; g.L = L; g.S = p->S; g.tpv = gp.tpv; g.QB = gp.QB;
-        g.seg_entries = gp.seg_entries;
+        g.B = p->B; g.V = p->V; g.Hh = p->Hh; g.W = p->W; g.H = p->H; g.L = L; g.S = p->S; g.tpv = gp.tpv; g.QB = gp.QB;
+        g.seg_entries = gp.seg_entries; g.A = gp.A;
         g.nslab = gp.nslab;
         g.err = err_word;
         switch (p->dtype) {

@@ -1,23 +1,31 @@
-// Backward, two-pass form: dK/dV as a GATHER over pixel-sorted sample lists.
+// Backward, two-pass form: dK/dV as a GATHER over sorted sample lists.
 //
 // The reference scatters every sample's contribution into dK/dV with scalar fp32
 // atomics (ops/triton.py:342-360; "TODO: reduce atomic conflict", ops/triton.py:341).
-// Here the same sums are formed without any atomic and in a fixed order:
+// Here the same sums are formed without colliding atomics and in a fixed order:
 //
 //   1. index_build_kernel   (per batch element, gather tile and key view; shared by all
-//      heads, since coordinates are, ops/torch.py:10): a counting sort of the tile's
-//      (sample, corner) pairs by key pixel.  Output per segment: row pointers [L+1] and
-//      entries {row offset of the query in the tile | index of the sample's scalars << 16,
-//      weight}, each pixel's entries in a fixed canonical order and padded with zero-weight
-//      entries to a multiple of four (the gather pass reads four entries per step).
+//      heads, since coordinates are, ops/torch.py:10): a counting sort of the tile's samples
+//      by ANCHOR.  The two corners of a sample that lie in one map row, (x0, y) and (x0+1, y),
+//      are neighbours in memory and receive the same query's rows, so they travel as one
+//      entry: anchor (y, a) with a = x0+1 in [0, W] stands for the pixel pair (a-1, a) of row y
+//      (a = 0 and a = W: one of the two lies outside the map and carries weight zero).  A sample
+//      gives up to two entries, one per map row of its footprint.  Output per segment: row
+//      pointers [A+1] over the A = H*(W+1) anchors and 16-byte entries {byte offset of the
+//      query's row in the tile, byte offset of the sample's scalars, weight of the left pixel,
+//      weight of the right pixel}, each anchor's entries in a fixed canonical order.
 //   2. bwd_scatter_kernel<..., TWOPASS>  (dsdpa_bwd.cuh): recomputes p and ds per sample,
 //      writes dq and the per-sample scalars (sm_scale*ds, p).
 //   3. bwd_gather_kernel    (per batch element, head and key view): for every gather tile
 //      loads the tile's q rows, dout rows and scalars into shared memory, then each group
-//      of lanes walks the entry list of one key pixel at a time, accumulating
+//      of lanes walks the entry list of one anchor at a time, accumulating for both pixels
 //          dK[pix] += (sm_scale*ds * w) * q[query],   dV[pix] += (p * w) * dout[query]
-//      in registers, and adds the result to the fp32 dK/dV maps in global memory, which
-//      this CTA alone owns (plain read-modify-write, tiles in order).
+//      in registers -- one read of the query's rows serves both -- and adds the sums to fp32
+//      maps in global memory.  A pixel is the left one of one anchor and the right one of the
+//      next, so there are two sets of maps, "left" and "right": every map element then has
+//      exactly one writer (the same lanes in every tile, in tile order), no two additions ever
+//      race, and the result is reproducible bit for bit.  After the last tile the CTA adds the
+//      two sets and hands the finished rows over (storage type, mirrors).
 //
 // A gather tile is a run of QB consecutive pixels of one query view (tpv tiles per view).
 #pragma once
@@ -28,26 +36,54 @@ namespace dsdpa {
 
 struct IndexParams {
     const float* coords;
-    int* rowptr;      // [B*T*V segments][L+1]
-    uint2* entries;   // [B*T*V segments][QB*S*4]
+    int* rowptr;      // [B*T*V segments][A+1]
+    uint4* entries;   // [B*T*V segments][seg_entries]
     int B, V, W, H, L, S;
     float hw, hh;
     int tpv, QB;      // T = V*tpv tiles per batch element
-    int rowb16;       // bytes of one q row in the gather tile / 16
-    int seg_entries;  // entries reserved per segment (QB*S*4 + 3*L, rounded up to 4)
+    int rowb;         // bytes of one q row in the gather tile
+    int seg_entries;  // entries reserved per segment (2*QB*S)
+    int A;            // anchors per map: H*(W+1)
+    int nhist;        // warps that take samples, each with a histogram of its own (1..NWARPS)
 };
 
 constexpr int kIndexWarpsDefault = 8;
 
-// Shared memory: cnt[NWARPS][L] ints, then part[NWARPS*32] ints.  (A template so that
+// One sample's footprint for the index: anchor column, the two map rows and the 1-D weights
+// (zero where the column / row lies outside the map), from the same arithmetic as
+// decode_corners, so that wx*wy reproduces the corner weights of the other kernels bit for bit.
+struct Footprint {
+    int a;            // x0 + 1
+    int y[2];
+    float wx[2], wy[2];
+};
+__device__ __forceinline__ void decode_footprint(float cx, float cy, int W, int H, float hw, float hh, Footprint& f) {
+    const float x = unnormalize(cx, hw), y = unnormalize(cy, hh);
+    const float xf = floorf(x), yf = floorf(y);
+    float fx = x - xf, fy = y - yf;
+    const bool xr = (xf >= -2.0f) && (xf <= (float)W + 1.0f);
+    const bool yr = (yf >= -2.0f) && (yf <= (float)H + 1.0f);
+    const int x0 = xr ? (int)xf : -2, y0 = yr ? (int)yf : -2;
+    if (!xr) fx = 0.0f;
+    if (!yr) fy = 0.0f;
+    const int x1 = x0 + 1, y1 = y0 + 1;
+    f.wx[0] = (x0 >= 0 && x0 < W) ? 1.0f - fx : 0.0f;
+    f.wx[1] = (x1 >= 0 && x1 < W) ? fx : 0.0f;
+    f.wy[0] = (y0 >= 0 && y0 < H) ? 1.0f - fy : 0.0f;
+    f.wy[1] = (y1 >= 0 && y1 < H) ? fy : 0.0f;
+    f.a = x1;
+    f.y[0] = y0;
+    f.y[1] = y1;
+}
+
+// Shared memory: cnt[nhist][A] ints, then part[NWARPS*32] ints.  (A template so that
 // the header can be included by several translation units.)
 template <int NWARPS>
 __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexParams p) {
     static_assert(NWARPS == 8, "the scan below handles 256 partial sums");
-    constexpr int kIndexWarps = NWARPS;
     extern __shared__ __align__(16) unsigned char smem[];
     int* cnt = reinterpret_cast<int*>(smem);
-    int* part = cnt + kIndexWarps * p.L;
+    int* part = cnt + p.nhist * p.A;
 
     const int T = p.V * p.tpv;
     const int seg = blockIdx.x;
@@ -59,12 +95,14 @@ __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexPar
     const int len = min(p.QB, p.L - l0);
     const int nsamp = len * p.S;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    // each warp owns a contiguous run of samples (a multiple of 32 of them)
-    const int per_warp = ((nsamp + kIndexWarps * 32 - 1) / (kIndexWarps * 32)) * 32;
-    const int wbeg = warp * per_warp, wend = min(wbeg + per_warp, nsamp);
-    int* mycnt = cnt + warp * p.L;
+    // each of the first nhist warps owns a contiguous run of samples (a multiple of 32 of them)
+    const int per_warp = ((nsamp + p.nhist * 32 - 1) / (p.nhist * 32)) * 32;
+    const int wbeg = warp < p.nhist ? min(warp * per_warp, nsamp) : nsamp;
+    const int wend = min(wbeg + per_warp, nsamp);
+    int* mycnt = cnt + (warp < p.nhist ? warp : 0) * p.A;
+    const int AW = p.W + 1;
 
-    for (int i = threadIdx.x; i < kIndexWarps * p.L; i += blockDim.x) cnt[i] = 0;
+    for (int i = threadIdx.x; i < p.nhist * p.A; i += blockDim.x) cnt[i] = 0;
     __syncthreads();
 
     // sample index (within the tile) -> coordinates; samples are ordered (query, s)
@@ -73,33 +111,39 @@ __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexPar
         const size_t row = ((((size_t)b * p.V + vq) * p.L + (l0 + ql)) * p.V + vk) * (size_t)p.S + s;
         return __ldg(reinterpret_cast<const float2*>(p.coords) + row);
     };
+    // the entry of map row r (0, 1) of a footprint: present iff one of its two weights is not zero
+    auto entry_of = [&](const Footprint& f, int r, float& wl, float& wr) -> int {
+        wl = f.wx[0] * f.wy[r];
+        wr = f.wx[1] * f.wy[r];
+        if (wl == 0.0f && wr == 0.0f) return -1;
+        return f.y[r] * AW + f.a;
+    };
 
-    // pass 1: per-warp histogram of key pixels
+    // pass 1: per-warp histogram of anchors
     for (int base = wbeg; base < wend; base += 32) {
         const int smp = base + lane;
         if (smp < wend) {
             const float2 c = coord_of(smp);
-            Corners cr;
-            float fx, fy;
-            decode_corners(c.x, c.y, p.W, p.H, p.hw, p.hh, cr, fx, fy);
+            Footprint f;
+            decode_footprint(c.x, c.y, p.W, p.H, p.hw, p.hh, f);
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-                if (cr.w[k] != 0.0f) atomicAdd(&mycnt[cr.pix[k]], 1);
+            for (int r = 0; r < 2; ++r) {
+                float wl, wr;
+                const int a = entry_of(f, r, wl, wr);
+                if (a >= 0) atomicAdd(&mycnt[a], 1);
+            }
         }
     }
     __syncthreads();
 
-    // pass 2: exclusive scan over pixels of the per-pixel totals -> row pointers, and
-    // per-warp start offsets inside each pixel's list (warp order = canonical order)
+    // pass 2: exclusive scan over anchors of the per-anchor totals -> row pointers, and
+    // per-warp start offsets inside each anchor's list (warp order = canonical order)
     const int nthr = blockDim.x;
-    const int chunk = (p.L + nthr - 1) / nthr;
-    const int pbeg = min((int)threadIdx.x * chunk, p.L), pend = min(pbeg + chunk, p.L);
+    const int chunk = (p.A + nthr - 1) / nthr;
+    const int pbeg = min((int)threadIdx.x * chunk, p.A), pend = min(pbeg + chunk, p.A);
     int local = 0;
-    for (int pix = pbeg; pix < pend; ++pix) {
-        int tot = 0;
-        for (int w = 0; w < kIndexWarps; ++w) tot += cnt[w * p.L + pix];
-        local += (tot + 3) & ~3;  // every list is padded to a multiple of four entries
-    }
+    for (int a = pbeg; a < pend; ++a)
+        for (int w = 0; w < p.nhist; ++w) local += cnt[w * p.A + a];
     part[threadIdx.x] = local;
     __syncthreads();
     if (warp == 0) {
@@ -118,66 +162,56 @@ __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexPar
         for (int i = 0; i < 8; ++i) { part[lane * 8 + i] = run; run += v[i]; }
     }
     __syncthreads();
-    int* rowptr = p.rowptr + (size_t)seg * (p.L + 1);
+    int* rowptr = p.rowptr + (size_t)seg * (p.A + 1);
     int run = part[threadIdx.x];
-    for (int pix = pbeg; pix < pend; ++pix) {
-        rowptr[pix] = run;
-        int at = run;
-        for (int w = 0; w < kIndexWarps; ++w) {
-            const int c = cnt[w * p.L + pix];
-            cnt[w * p.L + pix] = at;
-            at += c;
+    for (int a = pbeg; a < pend; ++a) {
+        rowptr[a] = run;
+        for (int w = 0; w < p.nhist; ++w) {
+            const int c = cnt[w * p.A + a];
+            cnt[w * p.A + a] = run;
+            run += c;
         }
-        run += (at - run + 3) & ~3;
     }
-    if (pend == p.L && pbeg < p.L) rowptr[p.L] = run;
-    if (p.L == 0 && threadIdx.x == 0) rowptr[0] = 0;
+    if (pend == p.A && pbeg < p.A) rowptr[p.A] = run;
     __syncthreads();
 
-    // pass 3: scatter in canonical order (32 samples at a time, corner-major inside),
-    // ranks of equal pixels inside the warp from match_any
-    uint2* entries = p.entries + (size_t)seg * (size_t)p.seg_entries;
+    // pass 3: scatter in canonical order (32 samples at a time, map row 0 before map row 1),
+    // ranks of equal anchors inside the warp from match_any
+    uint4* entries = p.entries + (size_t)seg * (size_t)p.seg_entries;
     for (int base = wbeg; base < wend; base += 32) {
         const int smp = base + lane;
-        Corners cr;
-        cr.w[0] = cr.w[1] = cr.w[2] = cr.w[3] = 0.0f;
-        cr.pix[0] = cr.pix[1] = cr.pix[2] = cr.pix[3] = 0;
-        unsigned tag = 0;
+        Footprint f;
+        f.a = 0; f.y[0] = f.y[1] = 0;
+        f.wx[0] = f.wx[1] = f.wy[0] = f.wy[1] = 0.0f;
+        uint32_t roff = 0, soff = 0;
         if (smp < wend) {
             const float2 c = coord_of(smp);
-            float fx, fy;
-            decode_corners(c.x, c.y, p.W, p.H, p.hw, p.hh, cr, fx, fy);
-            const int ql = smp / p.S;
-            // what the gather pass needs of the sample: where its query's row starts in the tile
-            // (in 16-byte units) and which of the tile's scalar pairs is its own
-            tag = (unsigned)(ql * p.rowb16) | ((unsigned)smp << 16);
+            decode_footprint(c.x, c.y, p.W, p.H, p.hw, p.hh, f);
+            // what the gather pass needs of the sample: where its query's row starts in the
+            // tile and where its pair of scalars lies among the tile's, both in bytes
+            roff = (uint32_t)(smp / p.S) * (uint32_t)p.rowb;
+            soff = (uint32_t)smp * 8u;
         }
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const bool valid = cr.w[k] != 0.0f;
+        for (int r = 0; r < 2; ++r) {
+            float wl, wr;
+            const int a = entry_of(f, r, wl, wr);
+            const bool valid = a >= 0;
             const unsigned vmask = __ballot_sync(0xffffffffu, valid);
             if (valid) {
-                const int pix = cr.pix[k];
-                const unsigned same = __match_any_sync(vmask, pix);
+                const unsigned same = __match_any_sync(vmask, a);
                 const int leader = __ffs(same) - 1;
                 const int rank = __popc(same & ((1u << lane) - 1u));
                 int start = 0;
                 if (lane == leader) {
-                    start = mycnt[pix];
-                    mycnt[pix] = start + __popc(same);
+                    start = mycnt[a];
+                    mycnt[a] = start + __popc(same);
                 }
                 start = __shfl_sync(same, start, leader);
-                entries[start + rank] = make_uint2(tag, __float_as_uint(cr.w[k]));
+                entries[start + rank] = make_uint4(roff, soff, __float_as_uint(wl), __float_as_uint(wr));
             }
             __syncwarp();
         }
-    }
-    __syncthreads();
-    // zero-weight padding behind every list (the last warp's cursor marks the list's end)
-    for (int pix = pbeg; pix < pend; ++pix) {
-        int at = cnt[(kIndexWarps - 1) * p.L + pix];
-        const int padded = (at + 3) & ~3;
-        for (; at < padded; ++at) entries[at] = make_uint2(0u, 0u);
     }
 }
 
@@ -186,89 +220,180 @@ struct GatherParams {
     const void* dout;
     const float2* scal;
     const int* rowptr;
-    const uint2* entries;
-    float* dk32;
-    float* dv32;
-    // where the finished maps go: dk/dv in the storage type (equal to dk32/dv32 for fp32 storage,
-    // which accumulates in place) and the optional mirrors (may be another GPU's memory)
+    const uint4* entries;
+    // fp32 accumulators [B,V,Hh,L,D]: contributions a pixel receives as the left / right one of
+    // an anchor.  (fp32 storage: the left maps are the dk/dv outputs themselves.)
+    float* dk_left;
+    float* dv_left;
+    float* dk_right;
+    float* dv_right;
+    // where the finished maps go: dk/dv in the storage type and the optional mirrors (may be
+    // another GPU's memory)
     void* dk;
     void* dv;
     void* dk_mirror;
     void* dv_mirror;
-    int B, V, Hh, L, S;
+    int B, V, Hh, W, H, L, S;
     int tpv, QB;
     int seg_entries;
-    int nslab;            // CTAs per (batch, head, key view)
+    int A;                // anchors per map: H*(W+1)
+    int nslab;            // CTAs per (batch, head, key view); each takes a run of map rows
     int* err;
 };
 
-// After the last tile: a group owns the same key pixels in every tile, and each lane the same
-// elements of their rows, so it hands its finished rows over itself (reading back what it wrote,
-// or the zero fill): rounded to the storage type into dK/dV, and into the mirrors.  These stores
-// are spread over the time the CTAs of the grid finish at.  (Everything it needs is derived
-// again from the block and thread index, so that nothing stays live across the tile loop for it.)
+// Unpacking of one 32-bit word of two 16-bit elements: the low / high element as fp32.
+__device__ __forceinline__ float word_lo(uint32_t w, __nv_bfloat16*) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float word_hi(uint32_t w, __nv_bfloat16*) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ float word_lo(uint32_t w, __half*) { return __half2float(__ushort_as_half((unsigned short)(w & 0xffffu))); }
+__device__ __forceinline__ float word_hi(uint32_t w, __half*) { return __half2float(__ushort_as_half((unsigned short)(w >> 16))); }
+
+// The accumulators of one anchor held by one lane: its EPL elements of the dK and dV rows of the
+// left and of the right pixel.
+//   16-bit storage: pairs (dK_e, dV_e), so that one packed fma serves both maps with the
+//     multiplier pair (a*w, p*w) and the operand pair (q_e, dout_e), which the unpacking writes
+//     side by side;
+//   fp32 storage: pairs of neighbouring elements (as they lie in the loaded row) per map.
 template <typename T, int D>
-__device__ __forceinline__ void gather_hand_over(const GatherParams& p) {
+struct AnchorAcc {
     using RC = RowCfg<T, D>;
-    constexpr int G = RC::G, NG = RC::NG, CH = RC::CH, EPV = RC::EPV, ROWB = RC::ROWB;
-    const bool narrow = sizeof(T) == 2;
-    if (!narrow && !p.dk_mirror && !p.dv_mirror) return;
-    // (read through volatile asm: the compiler then derives these values anew instead of
-    // carrying the tile loop's copies in registers through that loop)
-    unsigned tid, cta, ntid;
-    asm volatile("mov.u32 %0, %%tid.x;" : "=r"(tid));
-    asm volatile("mov.u32 %0, %%ctaid.x;" : "=r"(cta));
-    asm volatile("mov.u32 %0, %%ntid.x;" : "=r"(ntid));
-    const int lane = tid & 31, warp = tid >> 5, nw = ntid >> 5;
-    const int g = lane / G, li = lane % G;
-    const int slab = cta % p.nslab, unit = cta / p.nslab;
-    const int ngroups = nw * NG * p.nslab, gid = (warp * NG + g) * p.nslab + slab;
-    const size_t map = (size_t)unit / p.Hh % p.V + (size_t)p.V * (unit / (p.Hh * p.V));  // b*V + vk
-    const size_t map_row0 = (map * p.Hh + unit % p.Hh) * (size_t)p.L;
-    // one map after the other (K, then V) keeps the loop's register need small
-#pragma unroll 1
-    for (int which = 0; which < 2; ++which) {
-        const float* acc = (which ? p.dv32 : p.dk32) + map_row0 * D;
-        void* dst = which ? p.dv : p.dk;
-        void* mir = which ? p.dv_mirror : p.dk_mirror;
-        char* o_loc = narrow ? (char*)dst + map_row0 * ROWB : nullptr;
-        char* o_mir = mir ? (char*)mir + map_row0 * ROWB : nullptr;
-        if (!o_loc && !o_mir) continue;
-#pragma unroll 2
-        for (int pix = gid; pix < p.L; pix += ngroups) {
+    static constexpr bool NARROW = sizeof(T) == 2;
+    static constexpr int N = RC::EPL;   // float2 per side (both layouts)
+    float2 left[N], right[N];
+
+    __device__ __forceinline__ void clear() {
+#pragma unroll
+        for (int i = 0; i < N; ++i) left[i] = right[i] = make_float2(0.0f, 0.0f);
+    }
+
+    // One entry: rows of the entry's query at shared addresses q_row / do_row (this lane's first
+    // vector), multipliers (aL, pL) for the left pixel and (aR, pR) for the right one.
+    __device__ __forceinline__ void add(uint32_t q_row, uint32_t do_row, float aL, float pL, float aR, float pR) {
+        constexpr int G = RC::G, CH = RC::CH;
+        if constexpr (NARROW) {
+            const float2 mL = make_float2(aL, pL), mR = make_float2(aR, pR);
 #pragma unroll
             for (int ch = 0; ch < CH; ++ch) {
-                float f[EPV];
+                const uint4 rq = lds128(q_row + (uint32_t)(ch * G) * 16u), rd = lds128(do_row + (uint32_t)(ch * G) * 16u);
+                const uint32_t wq[4] = { rq.x, rq.y, rq.z, rq.w }, wd[4] = { rd.x, rd.y, rd.z, rd.w };
 #pragma unroll
-                for (int k = 0; k < EPV / 4; ++k) {
-                    const float4 a = *reinterpret_cast<const float4*>(acc + (size_t)pix * D + (size_t)(ch * G + li) * EPV + 4 * k);
-                    f[4 * k] = a.x; f[4 * k + 1] = a.y; f[4 * k + 2] = a.z; f[4 * k + 3] = a.w;
+                for (int i = 0; i < 4; ++i) {
+                    const float2 lo = make_float2(word_lo(wq[i], (T*)nullptr), word_lo(wd[i], (T*)nullptr));
+                    const float2 hi = make_float2(word_hi(wq[i], (T*)nullptr), word_hi(wd[i], (T*)nullptr));
+                    const int e = ch * 8 + 2 * i;
+                    left[e] = __ffma2_rn(mL, lo, left[e]);
+                    left[e + 1] = __ffma2_rn(mL, hi, left[e + 1]);
+                    right[e] = __ffma2_rn(mR, lo, right[e]);
+                    right[e + 1] = __ffma2_rn(mR, hi, right[e + 1]);
                 }
-                const uint4 packed = pack16(f, (T*)nullptr);
-                const size_t o = (size_t)pix * ROWB + (size_t)(ch * G + li) * 16;
-                if (o_loc) stg128(o_loc + o, packed);
-                if (o_mir) stg128(o_mir + o, packed);
             }
+        } else {
+            // layout per side: [ch][dK pair 0, dK pair 1, dV pair 0, dV pair 1]
+            const float2 aL2 = make_float2(aL, aL), pL2 = make_float2(pL, pL);
+            const float2 aR2 = make_float2(aR, aR), pR2 = make_float2(pR, pR);
+#pragma unroll
+            for (int ch = 0; ch < CH; ++ch) {
+                float2 fq[2], fd[2];
+                unpack16_pairs(lds128(q_row + (uint32_t)(ch * G) * 16u), fq, (T*)nullptr);
+                unpack16_pairs(lds128(do_row + (uint32_t)(ch * G) * 16u), fd, (T*)nullptr);
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    left[ch * 4 + k] = __ffma2_rn(aL2, fq[k], left[ch * 4 + k]);
+                    left[ch * 4 + 2 + k] = __ffma2_rn(pL2, fd[k], left[ch * 4 + 2 + k]);
+                    right[ch * 4 + k] = __ffma2_rn(aR2, fq[k], right[ch * 4 + k]);
+                    right[ch * 4 + 2 + k] = __ffma2_rn(pR2, fd[k], right[ch * 4 + 2 + k]);
+                }
+            }
+        }
+    }
+
+    // Adds one side to the rows of pixel `pix` of the dK / dV maps (this lane's elements).  Each
+    // element of these maps has a single writer, so the reduction is only a store that needs no
+    // read first.
+    __device__ __forceinline__ void flush_side(const float2 (&acc)[N], float* dkmap, float* dvmap, int pix, int li) const {
+        constexpr int G = RC::G, CH = RC::CH, EPV = RC::EPV;
+#pragma unroll
+        for (int ch = 0; ch < CH; ++ch) {
+            const size_t off = (size_t)pix * D + (size_t)(ch * G + li) * EPV;
+            if constexpr (NARROW) {
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    const int e = ch * 8 + 4 * k;
+                    red_global_add_v4(dkmap + off + 4 * k, acc[e].x, acc[e + 1].x, acc[e + 2].x, acc[e + 3].x);
+                    red_global_add_v4(dvmap + off + 4 * k, acc[e].y, acc[e + 1].y, acc[e + 2].y, acc[e + 3].y);
+                }
+            } else {
+                red_global_add_v4(dkmap + off, acc[ch * 4].x, acc[ch * 4].y, acc[ch * 4 + 1].x, acc[ch * 4 + 1].y);
+                red_global_add_v4(dvmap + off, acc[ch * 4 + 2].x, acc[ch * 4 + 2].y, acc[ch * 4 + 3].x, acc[ch * 4 + 3].y);
+            }
+        }
+    }
+};
+
+// After the last tile: the CTA adds the left and right maps of its map rows and hands the
+// finished rows over: rounded to the storage type into dK/dV, and into the mirrors.  These
+// stores are spread over the time the CTAs of the grid finish at.
+template <typename T, int D>
+__device__ __forceinline__ void gather_hand_over(const GatherParams& p, size_t map_row0, int pix_lo, int pix_hi) {
+    using RC = RowCfg<T, D>;
+    constexpr int EPV = RC::EPV, VEC = RC::VEC, ROWB = RC::ROWB;
+#pragma unroll 1
+    for (int which = 0; which < 2; ++which) {
+        const float* accl = (which ? p.dv_left : p.dk_left) + map_row0 * D;
+        const float* accr = (which ? p.dv_right : p.dk_right) + map_row0 * D;
+        char* o_loc = (char*)(which ? p.dv : p.dk) + map_row0 * ROWB;
+        void* mir = which ? p.dv_mirror : p.dk_mirror;
+        char* o_mir = mir ? (char*)mir + map_row0 * ROWB : nullptr;
+        // one 16-byte vector of the storage type per thread and step
+        const int nvec = (pix_hi - pix_lo) * VEC;
+        for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+            const size_t e0 = (size_t)pix_lo * D + (size_t)i * EPV;
+            float f[EPV];
+#pragma unroll
+            for (int k = 0; k < EPV / 4; ++k) {
+                const float4 a = __ldcg(reinterpret_cast<const float4*>(accl + e0) + k);
+                const float4 c = __ldcg(reinterpret_cast<const float4*>(accr + e0) + k);
+                f[4 * k] = a.x + c.x; f[4 * k + 1] = a.y + c.y; f[4 * k + 2] = a.z + c.z; f[4 * k + 3] = a.w + c.w;
+            }
+            const uint4 packed = pack16(f, (T*)nullptr);
+            const size_t o = (size_t)pix_lo * ROWB + (size_t)i * 16;
+            stg128(o_loc + o, packed);
+            if (o_mir) stg128(o_mir + o, packed);
         }
     }
 }
 
+// Entries travel from global memory to the lanes in chunks: the first kGatherChunk lanes of a
+// group load one entry each (one coalesced request, issued a whole chunk ahead of its use) and
+// park them in a small ring in shared memory, from which every lane of the group then reads
+// them one by one.  Two chunk buffers per group, and 16 bytes of padding so that the groups of
+// a warp, which tend to sit at the same position of their chunks, hit different banks.
+template <int G>
+struct GatherRing {
+    static constexpr int CHUNK = G < 8 ? G : 8;
+    static constexpr uint32_t STRIDE = 2u * CHUNK * 16u + 16u;   // bytes per group
+};
+
 // Shared memory of one tile: q rows and dout rows in the storage type ([QB, D] each), then
-// the tile's scalars ([QB, S] float2), then the mbarrier; all three filled by bulk copies.
+// the tile's scalars ([QB, S] float2), all three filled by bulk copies; then the mbarrier and
+// the groups' entry rings.
 template <typename T, int D>
 __global__ void __launch_bounds__(768, 1) bwd_gather_kernel(const GatherParams p) {
     using RC = RowCfg<T, D>;
-    constexpr int G = RC::G, NG = RC::NG, CH = RC::CH, EPV = RC::EPV, ROWB = RC::ROWB;
-    constexpr int HV = EPV / 2, HP = RC::EPL / 2;
+    constexpr int G = RC::G, NG = RC::NG, ROWB = RC::ROWB;
+    constexpr int CHUNK = GatherRing<G>::CHUNK;
     extern __shared__ __align__(128) unsigned char smem[];
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int g = lane / G, li = lane % G;
-    // (nslab > 1: several CTAs share one (batch, head, key view) and split its key pixels, which
+    const unsigned gmask = G == 32 ? 0xffffffffu : (((1u << (G & 31)) - 1u) << (g * G));
+    // (nslab > 1: several CTAs share one (batch, head, key view) and split its map rows, which
     // evens out the last wave of a small grid; each still loads every tile)
     const int slab = blockIdx.x % p.nslab, unit = blockIdx.x / p.nslab;
-    // groups of all CTAs that share the maps, and this group's rank among them
-    const int ngroups = nw * NG * p.nslab, gid = (warp * NG + g) * p.nslab + slab;
+    const int rows_per_slab = (p.H + p.nslab - 1) / p.nslab;
+    const int y_lo = min(slab * rows_per_slab, p.H), y_hi = min(y_lo + rows_per_slab, p.H);
+    const int AW = p.W + 1;
+    const int a_lo = y_lo * AW, a_hi = y_hi * AW;
+    const int ngroups = nw * NG, gid = warp * NG + g;
     // heads of one (batch, key view) are neighbours in the grid: they share the index
     const int h = unit % p.Hh;
     const int vk = (unit / p.Hh) % p.V;
@@ -280,6 +405,7 @@ __global__ void __launch_bounds__(768, 1) bwd_gather_kernel(const GatherParams p
     const uint32_t do_s = q_s + (uint32_t)p.QB * ROWB;
     const uint32_t sc_s = smem0 + 2u * (uint32_t)p.QB * ROWB;
     const uint32_t bar = sc_s + (((uint32_t)p.QB * p.S * 8u + 15u) & ~15u);
+    const uint32_t ring = bar + 16u + (uint32_t)gid * GatherRing<G>::STRIDE;
 
     if (threadIdx.x == 0) {
         mbar_init(bar, 1);
@@ -288,8 +414,14 @@ __global__ void __launch_bounds__(768, 1) bwd_gather_kernel(const GatherParams p
     }
     __syncthreads();
 
-    float* dkmap = p.dk32 + (((size_t)b * p.V + vk) * p.Hh + h) * (size_t)p.L * D;
-    float* dvmap = p.dv32 + (((size_t)b * p.V + vk) * p.Hh + h) * (size_t)p.L * D;
+    const size_t map_row0 = (((size_t)b * p.V + vk) * p.Hh + h) * (size_t)p.L;
+    float* dkl = p.dk_left + map_row0 * D;
+    float* dvl = p.dv_left + map_row0 * D;
+    float* dkr = p.dk_right + map_row0 * D;
+    float* dvr = p.dv_right + map_row0 * D;
+    // anchors are dealt round-robin to the groups; (ay, ax) follow the anchor index without a division
+    const int step_y = ngroups / AW, step_x = ngroups % AW;
+    unsigned chunk_no = 0;   // alternates the ring's two buffers; runs on across anchors and tiles
 
     for (int t = 0; t < NT; ++t) {
         const int vq = t / p.tpv, tl = t - vq * p.tpv;
@@ -313,98 +445,69 @@ __global__ void __launch_bounds__(768, 1) bwd_gather_kernel(const GatherParams p
 
         if (ok) {
             const size_t seg = ((size_t)b * NT + t) * p.V + vk;
-            const int* rowptr = p.rowptr + seg * (p.L + 1);
-            const uint4* entries4 = reinterpret_cast<const uint4*>(p.entries + seg * (size_t)p.seg_entries);
-            // Key pixels are dealt round-robin to the groups: neighbouring pixels have lists of
-            // similar length (also when the coordinates cluster), so the groups stay balanced.
-            // The walk is software-pipelined: the row pointers of the pixel after next and the
-            // first entries of the next pixel are requested before the current pixel's entries
-            // are processed, so that their L2 latency hides behind that work.
-            int pix = gid;
+            const int* rowptr = p.rowptr + seg * (p.A + 1);
+            const uint4* entries = p.entries + seg * (size_t)p.seg_entries;
+            // Neighbouring anchors have lists of similar length (also when the coordinates
+            // cluster), so dealing them round-robin keeps the groups balanced.  The walk is
+            // software-pipelined: the row pointers of the anchor after next and the first chunk
+            // of the next anchor's entries are requested before the current anchor's entries are
+            // processed, so that their L2 latency hides behind that work.
+            int a = a_lo + gid;
+            int ay = y_lo + gid / AW, ax = gid % AW;
             int beg = 0, end = 0, nbeg = 0, nend = 0;
-            if (pix < p.L) { beg = __ldg(rowptr + pix); end = __ldg(rowptr + pix + 1); }
-            if (pix + ngroups < p.L) { nbeg = __ldg(rowptr + pix + ngroups); nend = __ldg(rowptr + pix + ngroups + 1); }
-            uint4 first0 = make_uint4(0, 0, 0, 0), first1 = first0;
-            if (end > beg) { first0 = __ldg(entries4 + (beg >> 1)); first1 = __ldg(entries4 + (beg >> 1) + 1); }
-            while (pix < p.L) {
+            if (a < a_hi) { beg = __ldg(rowptr + a); end = __ldg(rowptr + a + 1); }
+            if (a + ngroups < a_hi) { nbeg = __ldg(rowptr + a + ngroups); nend = __ldg(rowptr + a + ngroups + 1); }
+            uint4 first = make_uint4(0, 0, 0, 0);
+            if (li < CHUNK && beg + li < end) first = __ldg(entries + beg + li);
+            while (a < a_hi) {
                 int n2beg = 0, n2end = 0;
-                if (pix + 2 * ngroups < p.L) {
-                    n2beg = __ldg(rowptr + pix + 2 * ngroups);
-                    n2end = __ldg(rowptr + pix + 2 * ngroups + 1);
+                if (a + 2 * ngroups < a_hi) {
+                    n2beg = __ldg(rowptr + a + 2 * ngroups);
+                    n2end = __ldg(rowptr + a + 2 * ngroups + 1);
                 }
-                uint4 nfirst0 = make_uint4(0, 0, 0, 0), nfirst1 = nfirst0;
-                if (nend > nbeg) { nfirst0 = __ldg(entries4 + (nbeg >> 1)); nfirst1 = __ldg(entries4 + (nbeg >> 1) + 1); }
+                uint4 nfirst = make_uint4(0, 0, 0, 0);
+                if (li < CHUNK && nbeg + li < nend) nfirst = __ldg(entries + nbeg + li);
                 if (end > beg) {
-                    // this CTA alone owns the (batch, head, key view) maps, so the update is a plain
-                    // read-modify-write; the read is issued now and hides behind the entry loop
-                    float4 gk[CH * (EPV / 4)], gv[CH * (EPV / 4)];
+                    AnchorAcc<T, D> acc;
+                    acc.clear();
+                    uint4 mine = first;   // this lane's entry of the chunk about to be processed
+                    for (int e0 = beg; e0 < end; e0 += CHUNK, ++chunk_no) {
+                        const uint32_t buf = ring + (chunk_no & 1u) * (uint32_t)(CHUNK * 16);
+                        if (li < CHUNK) sts128(buf + (uint32_t)li * 16u, mine);
+                        __syncwarp(gmask);
+                        if (li < CHUNK && e0 + CHUNK + li < end) mine = __ldg(entries + e0 + CHUNK + li);
+                        const int n = end - e0;
 #pragma unroll
-                    for (int ch = 0; ch < CH; ++ch)
-#pragma unroll
-                        for (int k = 0; k < EPV / 4; ++k) {
-                            const size_t off = (size_t)pix * D + (size_t)(ch * G + li) * EPV + 4 * k;
-                            gk[ch * (EPV / 4) + k] = *reinterpret_cast<const float4*>(dkmap + off);
-                            gv[ch * (EPV / 4) + k] = *reinterpret_cast<const float4*>(dvmap + off);
-                        }
-                    float2 ak[HP], av[HP];
-#pragma unroll
-                    for (int e = 0; e < HP; ++e) ak[e] = av[e] = make_float2(0.0f, 0.0f);
-                    // four entries (32 bytes) per step, the next four already in flight; lists are
-                    // padded to a multiple of four with zero-weight entries
-                    uint4 nx0 = first0, nx1 = first1;
-                    for (int e0 = beg; e0 < end; e0 += 4) {
-                        const uint4 c0 = nx0, c1 = nx1;
-                        if (e0 + 4 < end) {
-                            nx0 = __ldg(entries4 + ((e0 + 4) >> 1));
-                            nx1 = __ldg(entries4 + ((e0 + 4) >> 1) + 1);
-                        }
-                        const uint32_t tags[4] = { c0.x, c0.z, c1.x, c1.z };
-                        const float ws[4] = { __uint_as_float(c0.y), __uint_as_float(c0.w), __uint_as_float(c1.y),
-                                              __uint_as_float(c1.w) };
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const uint32_t roff = (tags[u] & 0xffffu) << 4, soff = (tags[u] >> 16) << 3;
-                            float2 sc;
-                            asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(sc.x), "=f"(sc.y) : "r"(sc_s + soff));
-                            const float aw = sc.x * ws[u], pw = sc.y * ws[u];
-                            const float2 aw2 = make_float2(aw, aw), pw2 = make_float2(pw, pw);
-#pragma unroll
-                            for (int ch = 0; ch < CH; ++ch) {
-                                float2 fq[HV], fd[HV];
-                                unpack16_pairs(lds128(q_s + roff + (uint32_t)(ch * G) * 16u), fq, (T*)nullptr);
-                                unpack16_pairs(lds128(do_s + roff + (uint32_t)(ch * G) * 16u), fd, (T*)nullptr);
-#pragma unroll
-                                for (int k = 0; k < HV; ++k) {
-                                    ak[ch * HV + k] = __ffma2_rn(aw2, fq[k], ak[ch * HV + k]);
-                                    av[ch * HV + k] = __ffma2_rn(pw2, fd[k], av[ch * HV + k]);
-                                }
+                        for (int i = 0; i < CHUNK; ++i) {
+                            if (i < n) {
+                                const uint4 ent = lds128(buf + (uint32_t)i * 16u);
+                                float2 sc;
+                                asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(sc.x), "=f"(sc.y) : "r"(sc_s + ent.y));
+                                const float wl = __uint_as_float(ent.z), wr = __uint_as_float(ent.w);
+                                acc.add(q_s + ent.x, do_s + ent.x, sc.x * wl, sc.y * wl, sc.x * wr, sc.y * wr);
                             }
                         }
                     }
-#pragma unroll
-                    for (int ch = 0; ch < CH; ++ch)
-#pragma unroll
-                        for (int k = 0; k < EPV / 4; ++k) {
-                            const size_t off = (size_t)pix * D + (size_t)(ch * G + li) * EPV + 4 * k;
-                            float4 a = gk[ch * (EPV / 4) + k], c = gv[ch * (EPV / 4) + k];
-                            const int e = ch * HV + 2 * k;
-                            a.x += ak[e].x; a.y += ak[e].y; a.z += ak[e + 1].x; a.w += ak[e + 1].y;
-                            c.x += av[e].x; c.y += av[e].y; c.z += av[e + 1].x; c.w += av[e + 1].y;
-                            *reinterpret_cast<float4*>(dkmap + off) = a;
-                            *reinterpret_cast<float4*>(dvmap + off) = c;
-                        }
+                    const int pix = ay * p.W + ax;  // the right pixel; the left one is pix - 1
+                    if (ax > 0) acc.flush_side(acc.left, dkl, dvl, pix - 1, li);
+                    if (ax < p.W) acc.flush_side(acc.right, dkr, dvr, pix, li);
                 }
-                pix += ngroups;
+                a += ngroups;
+                ay += step_y; ax += step_x;
+                if (ax >= AW) { ax -= AW; ++ay; }
                 beg = nbeg; end = nend;
                 nbeg = n2beg; nend = n2end;
-                first0 = nfirst0; first1 = nfirst1;
+                first = nfirst;
             }
         }
         // every group is done with the tile before its buffers are refilled
         if (__syncthreads_or(ok ? 0 : 1)) return;
     }
 
-    gather_hand_over<T, D>(p);
+    // the additions of all groups reach memory before any thread reads the maps back
+    __threadfence();
+    __syncthreads();
+    gather_hand_over<T, D>(p, map_row0, y_lo * p.W, y_hi * p.W);
 }
 
 }  // namespace dsdpa

@@ -13,6 +13,7 @@ namespace dsdpa {
 constexpr int kPlanSMs = 148;
 constexpr int kPlanSmemMax = 232448;
 constexpr int kPlanRecBytesPerWarp = 1024;
+constexpr int kGatherMaxThreads = 768;   // what bwd_gather_kernel is compiled for
 
 inline int dtype_size(int dtype) { return dtype == DSDPA_F32 ? 4 : 2; }
 
@@ -48,7 +49,9 @@ struct GatherPlan {
     int QB;             // queries (pixels of one query view) per gather tile, even
     int gather_threads;
     size_t gather_smem;
-    int nslab;               // CTAs that split the key pixels of one (batch, head, key view)
+    int A;                   // anchors per map, H*(W+1): the lists the index is sorted into
+    int nhist;               // histograms (sample-taking warps) of the index builder
+    int nslab;               // CTAs that split the map rows of one (batch, head, key view)
     long long gather_ctas;   // B*Hh*V*nslab
     long long segments;      // B * (V*tpv) * V index segments
     int seg_entries;         // index entries reserved per segment

@@ -10,6 +10,8 @@ Triton.
 from __future__ import annotations
 
 import ctypes
+import os
+import warnings
 
 import torch
 
@@ -19,6 +21,13 @@ _DTYPES = {torch.float32: cabi.F32, torch.bfloat16: cabi.BF16, torch.float16: ca
 
 # Process-wide default flags (DSDPA_FLAG_*), e.g. to force a path in tests.
 default_flags = 0
+
+# Debug aid, off by default: when set (or with DSDPA_CHECK_DEVICE_ERRORS=1 in the environment),
+# the autograd function synchronises the device after every backward and raises if a kernel
+# recorded that one of its bounded waits ran out (such a kernel returns without writing its
+# results).  Without it nobody looks at that record unless the caller polls
+# ``cabi.lib().dsdpa_device_error(device)`` itself.
+check_device_errors = os.environ.get("DSDPA_CHECK_DEVICE_ERRORS", "0") not in ("", "0")
 
 
 def _problem(q, coords, W, H, sm_scale, flags) -> cabi.Problem:
@@ -141,8 +150,18 @@ class _FusedDeformSDPA(torch.autograd.Function):
     def backward(ctx, do):
         q, k, v, coords, out, lse = ctx.saved_tensors
         want_dc = ctx.needs_input_grad[3]
+        if want_dc:
+            # the coordinate gradient rides on the two-pass form; where that form cannot run (a map
+            # too large for its index builder, scatter flags) coords get None, as in the reference
+            prob = _problem(q, coords, ctx.WIDTH, ctx.HEIGHT, ctx.sm_scale, default_flags)
+            if not cabi.lib().dsdpa_backward_supports_dcoords(ctypes.byref(prob)):
+                warnings.warn("deform_sdpa: the coordinate gradient is not available for this problem "
+                              "(scatter form of the backward); coords receive no gradient", UserWarning, stacklevel=2)
+                want_dc = False
         dq, dk, dv, dc = backward_raw(q, k, v, coords, out, lse, do, ctx.WIDTH, ctx.HEIGHT, ctx.sm_scale,
                                       want_dcoords=want_dc)
+        if check_device_errors:
+            cabi.check(cabi.lib().dsdpa_device_error(q.device.index))
         if dc is not None and dc.dtype != coords.dtype:
             dc = dc.to(coords.dtype)
         # ops/triton.py:464 returns (dq, dk, dv, None, None, None, None)

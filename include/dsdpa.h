@@ -96,6 +96,15 @@ int dsdpa_forward(const dsdpa_problem* p,
 size_t dsdpa_backward_workspace_bytes(const dsdpa_problem* p);
 
 /*
+ * 1 if dsdpa_backward can produce the coordinate gradient (its `dcoords` argument) for this
+ * problem, 0 if not: the gradient is computed by the two-pass form only, and problems that form
+ * cannot take (a map too large for its index builder, or the scatter flags) are refused with
+ * DSDPA_ERR_BAD_FLAGS when dcoords is given.  The reference never returns this gradient
+ * (ops/triton.py:464 returns None for coords); callers that may not get it ask here first.
+ */
+int dsdpa_backward_supports_dcoords(const dsdpa_problem* p);
+
+/*
  * Backward.  Replaces _fused_deform_sdpa.backward's device work (ops/triton.py:419-464):
  * delta = sum(out*dout) (ops/triton.py:197-215), dq (ops/triton.py:339, 362-365) and the
  * dK/dV scatter (ops/triton.py:342-360), including the zero fill of the accumulators and

@@ -5,6 +5,8 @@ under tests/golden; the configuration cases compare against the CPU oracle on th
 seeded inputs.  Tolerances are the ones stated for the path: 1e-4 (max-norm relative)
 for fp32 storage, 2e-2 for 16-bit storage with fp32 accumulation.
 """
+import ctypes
+
 import pytest
 import torch
 
@@ -230,16 +232,41 @@ def test_non_contiguous_inputs_are_accepted(backend):
     assert rel_err(out, c["out"]) < 1e-4
 
 
-def test_large_map_falls_back_to_the_scatter_backward(backend, oracle):
-    """A map of more than ~7000 pixels does not fit the index builder's shared memory: the
-    backward then runs the scatter form by itself (and refuses a coordinate gradient)."""
+def test_large_map_runs_the_two_pass_backward_with_fewer_histograms(backend, oracle):
+    """A map of 8000 pixels does not leave the index builder room for eight histograms: it
+    builds the same lists with fewer, and the two-pass form (coordinate gradient included) runs."""
     B, V, Hh, W, H, D, S = 1, 2, 1, 100, 80, 16, 2
     g = torch.Generator().manual_seed(5)
     L = W * H
     q, k, v, dout = (torch.randn(B, V, Hh, L, D, generator=g) for _ in range(4))
     coords = torch.rand(B, V, L, V, S, 2, generator=g) * 1.1 - 0.05
     text = backend.cabi.describe_plan(backend.cabi.Problem(B, V, Hh, W, H, D, S, 0.25, backend.cabi.F32, 0))
+    assert "bwd_pass_a[" in text and "bwd_gather" in text
+    out, lse, dq, dk, dv = _run(backend, (q, k, v, coords, dout), 0, torch.float32, W, H, 0.25)
+    o_ref, _ = oracle.forward(q, k, v, coords, W, H, 0.25)
+    dq_ref, dk_ref, dv_ref, dc_ref = oracle.backward(q, k, v, coords, dout, W, H, 0.25, with_dcoords=True)
+    assert rel_err(out, o_ref) < 1e-4 and rel_err(dq, dq_ref) < 1e-4
+    assert rel_err(dk, dk_ref) < 1e-4 and rel_err(dv, dv_ref) < 1e-4
+    dev = torch.device("cuda", 0)
+    *_, dc = backend.backward_raw(q.to(dev), k.to(dev), v.to(dev), coords.to(dev), out, lse, dout.to(dev), W, H, 0.25,
+                                  want_dcoords=True)
+    assert rel_err(dc, dc_ref) < 1e-4
+
+
+def test_huge_map_falls_back_to_the_scatter_backward(backend, oracle):
+    """A map whose anchors do not fit even one histogram in shared memory (here 250x240) runs
+    the scatter form by itself.  That form has no coordinate gradient: the C ABI refuses one,
+    and the autograd function returns None for coords, as the reference does
+    (ops/triton.py:464), with a warning."""
+    B, V, Hh, W, H, D, S = 1, 1, 1, 250, 240, 16, 2
+    g = torch.Generator().manual_seed(6)
+    L = W * H
+    q, k, v, dout = (torch.randn(B, V, Hh, L, D, generator=g) for _ in range(4))
+    coords = torch.rand(B, V, L, V, S, 2, generator=g) * 1.1 - 0.05
+    prob = backend.cabi.Problem(B, V, Hh, W, H, D, S, 0.25, backend.cabi.F32, 0)
+    text = backend.cabi.describe_plan(prob)
     assert "bwd_scatter[" in text and "bwd_gather" not in text
+    assert backend.cabi.lib().dsdpa_backward_supports_dcoords(ctypes.byref(prob)) == 0
     out, lse, dq, dk, dv = _run(backend, (q, k, v, coords, dout), 0, torch.float32, W, H, 0.25)
     o_ref, _ = oracle.forward(q, k, v, coords, W, H, 0.25)
     dq_ref, dk_ref, dv_ref, _ = oracle.backward(q, k, v, coords, dout, W, H, 0.25)
@@ -249,6 +276,12 @@ def test_large_map_falls_back_to_the_scatter_backward(backend, oracle):
     with pytest.raises(ValueError):
         backend.backward_raw(q.to(dev), k.to(dev), v.to(dev), coords.to(dev), out, lse, dout.to(dev), W, H, 0.25,
                              want_dcoords=True)
+    # through autograd a training step still runs: coords get no gradient
+    from ops.triton import deform_sdpa_triton
+    qd, kd, vd, cd = (t.to(dev).requires_grad_(True) for t in (q, k, v, coords))
+    with pytest.warns(UserWarning, match="coordinate gradient"):
+        deform_sdpa_triton(qd, kd, vd, cd, W, H, 0.25).backward(dout.to(dev))
+    assert cd.grad is None and rel_err(qd.grad, dq_ref) < 1e-4 and rel_err(kd.grad, dk_ref) < 1e-4
 
 
 @pytest.mark.parametrize("flagname", ["default", "scatter", "scatter_global"])
