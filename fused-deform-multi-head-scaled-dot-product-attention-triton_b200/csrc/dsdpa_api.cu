@@ -163,10 +163,12 @@ GatherPlan plan_gather(const dsdpa_problem& p) {
     while (qb_max > 2 && qb_max * p.S * 2 > (1ll << 30)) qb_max -= 2;
     // The index builder keeps one histogram over the anchors per sample-taking warp: eight when
     // they fit, fewer for large maps (slower to build, same lists).
-    long long nhist = ((long long)kPlanSmemMax - 1024) / (A * 4);
+    // (beside the histograms: the lists' first entries [A], 256 partial sums, the length buckets)
+    const long long fixed_ints = 256 + (long long)kMaxSlabs * kLenBuckets;
+    long long nhist = ((long long)kPlanSmemMax / 4 - 16 - fixed_ints) / A - 1;
     if (nhist > 8) nhist = 8;
     if (qb_max < 2 || nhist < 1 || A + 1 >= (1ll << 30)) return g;  // ok = false
-    size_t index_smem = ((size_t)nhist * A + 256) * sizeof(int);
+    size_t index_smem = (size_t)((nhist + 1) * A + fixed_ints) * sizeof(int);
     {
         // The index builder scatters 16-byte entries; with many CTAs per SM their half-written
         // 32-byte sectors outgrow L2 and are evicted before they are complete.  Asking for more
@@ -190,7 +192,7 @@ GatherPlan plan_gather(const dsdpa_problem& p) {
         const long long units = (long long)p.B * p.Hh * p.V;
         int best = 1;
         double best_eff = 0.0;
-        for (int ns = 1; ns <= 4 && ns <= p.H; ++ns) {
+        for (int ns = 1; ns <= kMaxSlabs && ns <= p.H; ++ns) {
             const long long ctas = units * ns;
             const long long waves = (ctas + kPlanSMs - 1) / kPlanSMs;
             // every extra CTA of a unit reloads the tiles (2% per split), and the slabs are whole
@@ -201,7 +203,7 @@ GatherPlan plan_gather(const dsdpa_problem& p) {
             if (eff > best_eff + 1e-9) { best_eff = eff; best = ns; }
         }
         const int force = knobs().gather_nslab;
-        g.nslab = force >= 1 && force <= 8 && force <= p.H ? force : best;
+        g.nslab = force >= 1 && force <= kMaxSlabs && force <= p.H ? force : best;
         g.gather_ctas = units * g.nslab;
     }
     const long long T = (long long)p.V * g.tpv;
@@ -210,7 +212,8 @@ GatherPlan plan_gather(const dsdpa_problem& p) {
     g.scal_bytes = (((size_t)p.B * p.Hh * T * p.V * qb * p.S * 8) + 16 + 255) & ~(size_t)255;
     g.seg_entries = (int)((long long)qb * p.S * 2);
     g.entries_bytes = (((size_t)g.segments * g.seg_entries * 16) + 255) & ~(size_t)255;
-    g.rowptr_bytes = (((size_t)g.segments * (A + 1) * 4) + 255) & ~(size_t)255;
+    g.sched_bytes = (((size_t)g.segments * A * 16) + 255) & ~(size_t)255;
+    g.hdr_bytes = (((size_t)g.segments * g.nslab * 8) + 255) & ~(size_t)255;
     return g;
 }
 
@@ -400,7 +403,7 @@ size_t dsdpa_backward_workspace_bytes(const dsdpa_problem* p) {
     const GatherPlan g = plan_gather(*p);
     const bool two = use_two_pass(*p, g);
     size_t bytes = accumulator_bytes(*p, two);
-    if (two) bytes += g.scal_bytes + g.entries_bytes + g.rowptr_bytes;
+    if (two) bytes += g.scal_bytes + g.entries_bytes + g.sched_bytes + g.hdr_bytes;
     return bytes;
 }
 
@@ -466,16 +469,17 @@ int dsdpa_backward_mirrored(const dsdpa_problem* p, const void* q, const void* k
     char* ws = (char*)workspace + acc_bytes;
     float2* scal = two_pass ? (float2*)ws : nullptr;
     uint4* entries = two_pass ? (uint4*)(ws + gp.scal_bytes) : nullptr;
-    int* rowptr = two_pass ? (int*)(ws + gp.scal_bytes + gp.entries_bytes) : nullptr;
+    int4* sched = two_pass ? (int4*)(ws + gp.scal_bytes + gp.entries_bytes) : nullptr;
+    int2* sched_hdr = two_pass ? (int2*)(ws + gp.scal_bytes + gp.entries_bytes + gp.sched_bytes) : nullptr;
 
     if (two_pass) {
         // pixel-sorted sample lists, shared by all heads
         IndexParams ip{};
-        ip.coords = coords; ip.rowptr = rowptr; ip.entries = entries;
+        ip.coords = coords; ip.sched = sched; ip.sched_hdr = sched_hdr; ip.entries = entries;
         ip.B = p->B; ip.V = p->V; ip.W = p->W; ip.H = p->H; ip.L = L; ip.S = p->S;
         ip.hw = hw; ip.hh = hh; ip.tpv = gp.tpv; ip.QB = gp.QB;
         ip.rowb = p->D * dtype_size(p->dtype); ip.seg_entries = gp.seg_entries;
-        ip.A = gp.A; ip.nhist = gp.nhist;
+        ip.A = gp.A; ip.nhist = gp.nhist; ip.nslab = gp.nslab;
         static bool index_attr[64] = {};
         if ((e = detail::allow_big_smem(index_build_kernel<kIndexWarpsDefault>, index_attr)) != cudaSuccess) return cuda_fail(e);
         index_build_kernel<kIndexWarpsDefault><<<(unsigned)gp.segments, kIndexWarpsDefault * 32, gp.index_smem, s>>>(ip);
@@ -511,7 +515,7 @@ int dsdpa_backward_mirrored(const dsdpa_problem* p, const void* q, const void* k
 
     if (two_pass) {
         GatherParams g{};
-        g.q = q; g.dout = dout; g.scal = scal; g.rowptr = rowptr; g.entries = entries;
+        g.q = q; g.dout = dout; g.scal = scal; g.sched = sched; g.sched_hdr = sched_hdr; g.entries = entries;
         g.dk_left = dk32; g.dv_left = dv32; g.dk_right = dk_right; g.dv_right = dv_right;
         g.dk = dk; g.dv = dv; g.dk_mirror = mir.dk; g.dv_mirror = mir.dv;
         g.B = p->B; g.V = p->V; g.Hh = p->Hh; g.W = p->W; g.H = p->H; g.L = L; g.S = p->S; g.tpv = gp.tpv; g.QB = gp.QB;

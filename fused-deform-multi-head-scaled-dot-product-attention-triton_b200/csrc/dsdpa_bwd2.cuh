@@ -10,10 +10,13 @@
 //      are neighbours in memory and receive the same query's rows, so they travel as one
 //      entry: anchor (y, a) with a = x0+1 in [0, W] stands for the pixel pair (a-1, a) of row y
 //      (a = 0 and a = W: one of the two lies outside the map and carries weight zero).  A sample
-//      gives up to two entries, one per map row of its footprint.  Output per segment: row
-//      pointers [A+1] over the A = H*(W+1) anchors and 16-byte entries {byte offset of the
-//      query's row in the tile, byte offset of the sample's scalars, weight of the left pixel,
-//      weight of the right pixel}, each anchor's entries in a fixed canonical order.
+//      gives up to two entries, one per map row of its footprint.  Output per segment: 16-byte
+//      entries {byte offset of the query's row in the tile, byte offset of the sample's scalars,
+//      weight of the left pixel, weight of the right pixel}, each anchor's entries in a fixed
+//      canonical order, and a work list of the non-empty anchors {right pixel, first entry, end,
+//      column} sorted by list length, longest first (per slab of map rows when several CTAs
+//      share a map): lanes that work side by side then get lists of equal length, and dealing
+//      the sorted list out back and forth gives every group the same amount of work.
 //   2. bwd_scatter_kernel<..., TWOPASS>  (dsdpa_bwd.cuh): recomputes p and ds per sample,
 //      writes dq and the per-sample scalars (sm_scale*ds, p).
 //   3. bwd_gather_kernel    (per batch element, head and key view): for every gather tile
@@ -36,7 +39,8 @@ namespace dsdpa {
 
 struct IndexParams {
     const float* coords;
-    int* rowptr;      // [B*T*V segments][A+1]
+    int4* sched;      // [B*T*V segments][A] work list: {right pixel, first entry, end, anchor column}
+    int2* sched_hdr;  // [B*T*V segments][nslab] {first record of the slab, non-empty anchors in it}
     uint4* entries;   // [B*T*V segments][seg_entries]
     int B, V, W, H, L, S;
     float hw, hh;
@@ -45,7 +49,11 @@ struct IndexParams {
     int seg_entries;  // entries reserved per segment (2*QB*S)
     int A;            // anchors per map: H*(W+1)
     int nhist;        // warps that take samples, each with a histogram of its own (1..NWARPS)
+    int nslab;        // slabs of map rows the gather pass splits a map into (1..kMaxSlabs)
 };
+
+constexpr int kMaxSlabs = 4;
+constexpr int kLenBuckets = 512;   // list lengths are sorted exactly up to this, longer ones count as equal
 
 constexpr int kIndexWarpsDefault = 8;
 
@@ -76,14 +84,16 @@ __device__ __forceinline__ void decode_footprint(float cx, float cy, int W, int 
     f.y[1] = y1;
 }
 
-// Shared memory: cnt[nhist][A] ints, then part[NWARPS*32] ints.  (A template so that
-// the header can be included by several translation units.)
+// Shared memory: cnt[nhist][A] ints, then lens[A], part[NWARPS*32], bucket[nslab*kLenBuckets]
+// ints.  (A template so that the header can be included by several translation units.)
 template <int NWARPS>
 __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexParams p) {
     static_assert(NWARPS == 8, "the scan below handles 256 partial sums");
     extern __shared__ __align__(16) unsigned char smem[];
     int* cnt = reinterpret_cast<int*>(smem);
-    int* part = cnt + p.nhist * p.A;
+    int* lens = cnt + p.nhist * p.A;       // first entry of every anchor's list, later its length
+    int* part = lens + p.A;
+    int* bucket = part + NWARPS * 32;
 
     const int T = p.V * p.tpv;
     const int seg = blockIdx.x;
@@ -162,17 +172,16 @@ __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexPar
         for (int i = 0; i < 8; ++i) { part[lane * 8 + i] = run; run += v[i]; }
     }
     __syncthreads();
-    int* rowptr = p.rowptr + (size_t)seg * (p.A + 1);
     int run = part[threadIdx.x];
     for (int a = pbeg; a < pend; ++a) {
-        rowptr[a] = run;
+        lens[a] = run;
         for (int w = 0; w < p.nhist; ++w) {
             const int c = cnt[w * p.A + a];
             cnt[w * p.A + a] = run;
             run += c;
         }
     }
-    if (pend == p.A && pbeg < p.A) rowptr[p.A] = run;
+    for (int i = threadIdx.x; i < p.nslab * kLenBuckets; i += blockDim.x) bucket[i] = 0;
     __syncthreads();
 
     // pass 3: scatter in canonical order (32 samples at a time, map row 0 before map row 1),
@@ -213,13 +222,75 @@ __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexPar
             __syncwarp();
         }
     }
+    __syncthreads();
+
+    // pass 4: the work list.  Counting sort of the anchors by (slab of map rows, list length
+    // descending); empty lists end up behind each slab's non-empty ones and are not written.
+    // (Anchors of equal length land in arbitrary order: which group of lanes works on an anchor
+    // does not change any sum.)
+    const int rows_per_slab = (p.H + p.nslab - 1) / p.nslab;
+    auto bucket_of = [&](int a, int len) -> int {
+        const int slab = (a / AW) / rows_per_slab;
+        return slab * kLenBuckets + (kLenBuckets - 1 - min(len, kLenBuckets - 1));
+    };
+    for (int a = pbeg; a < pend; ++a) {
+        // the last histogram's cursor has run to the end of the anchor's list
+        const int len = cnt[(p.nhist - 1) * p.A + a] - lens[a];
+        atomicAdd(&bucket[bucket_of(a, len)], 1);
+    }
+    __syncthreads();
+    {
+        const int nb = p.nslab * kLenBuckets, per = (nb + nthr - 1) / nthr;   // buckets per thread
+        const int b0 = min((int)threadIdx.x * per, nb), b1 = min(b0 + per, nb);
+        int sum = 0;
+        for (int i = b0; i < b1; ++i) sum += bucket[i];
+        part[threadIdx.x] = sum;
+        __syncthreads();
+        if (warp == 0) {
+            int v[8], tot = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { v[i] = part[lane * 8 + i]; tot += v[i]; }
+            int incl = tot;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int n = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += n;
+            }
+            int r2 = incl - tot;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { part[lane * 8 + i] = r2; r2 += v[i]; }
+        }
+        __syncthreads();
+        int at = part[threadIdx.x];
+        for (int i = b0; i < b1; ++i) {
+            const int c = bucket[i];
+            bucket[i] = at;
+            at += c;
+        }
+        __syncthreads();
+        if ((int)threadIdx.x < p.nslab) {
+            const int first = bucket[threadIdx.x * kLenBuckets];
+            p.sched_hdr[(size_t)seg * p.nslab + threadIdx.x] =
+                make_int2(first, bucket[threadIdx.x * kLenBuckets + kLenBuckets - 1] - first);
+        }
+        __syncthreads();   // the headers are read before the cursors move
+    }
+    int4* sched = p.sched + (size_t)seg * p.A;
+    for (int a = pbeg; a < pend; ++a) {
+        const int beg = lens[a], end = cnt[(p.nhist - 1) * p.A + a];
+        if (end == beg) continue;
+        const int pos = atomicAdd(&bucket[bucket_of(a, end - beg)], 1);
+        const int ay = a / AW, ax = a - ay * AW;
+        sched[pos] = make_int4(ay * p.W + ax, beg, end, ax);
+    }
 }
 
 struct GatherParams {
     const void* q;
     const void* dout;
     const float2* scal;
-    const int* rowptr;
+    const int4* sched;
+    const int2* sched_hdr;
     const uint4* entries;
     // fp32 accumulators [B,V,Hh,L,D]: contributions a pixel receives as the left / right one of
     // an anchor.  (fp32 storage: the left maps are the dk/dv outputs themselves.)
@@ -242,8 +313,9 @@ struct GatherParams {
 };
 
 // Unpacking of one 32-bit word of two 16-bit elements: the low / high element as fp32.
-__device__ __forceinline__ float word_lo(uint32_t w, __nv_bfloat16*) { return __uint_as_float(w << 16); }
-__device__ __forceinline__ float word_hi(uint32_t w, __nv_bfloat16*) { return __uint_as_float(w & 0xffff0000u); }
+// (bf16: byte permutes, which run on the integer pipe and leave the fma pipe to the fmas)
+__device__ __forceinline__ float word_lo(uint32_t w, __nv_bfloat16*) { return __uint_as_float(__byte_perm(w, 0u, 0x1044)); }
+__device__ __forceinline__ float word_hi(uint32_t w, __nv_bfloat16*) { return __uint_as_float(__byte_perm(w, 0u, 0x3244)); }
 __device__ __forceinline__ float word_lo(uint32_t w, __half*) { return __half2float(__ushort_as_half((unsigned short)(w & 0xffffu))); }
 __device__ __forceinline__ float word_hi(uint32_t w, __half*) { return __half2float(__ushort_as_half((unsigned short)(w >> 16))); }
 
@@ -391,8 +463,6 @@ __global__ void __launch_bounds__(768, 1) bwd_gather_kernel(const GatherParams p
     const int slab = blockIdx.x % p.nslab, unit = blockIdx.x / p.nslab;
     const int rows_per_slab = (p.H + p.nslab - 1) / p.nslab;
     const int y_lo = min(slab * rows_per_slab, p.H), y_hi = min(y_lo + rows_per_slab, p.H);
-    const int AW = p.W + 1;
-    const int a_lo = y_lo * AW, a_hi = y_hi * AW;
     const int ngroups = nw * NG, gid = warp * NG + g;
     // heads of one (batch, key view) are neighbours in the grid: they share the index
     const int h = unit % p.Hh;
@@ -419,8 +489,6 @@ __global__ void __launch_bounds__(768, 1) bwd_gather_kernel(const GatherParams p
     float* dvl = p.dv_left + map_row0 * D;
     float* dkr = p.dk_right + map_row0 * D;
     float* dvr = p.dv_right + map_row0 * D;
-    // anchors are dealt round-robin to the groups; (ay, ax) follow the anchor index without a division
-    const int step_y = ngroups / AW, step_x = ngroups % AW;
     unsigned chunk_no = 0;   // alternates the ring's two buffers; runs on across anchors and tiles
 
     for (int t = 0; t < NT; ++t) {
@@ -445,28 +513,31 @@ __global__ void __launch_bounds__(768, 1) bwd_gather_kernel(const GatherParams p
 
         if (ok) {
             const size_t seg = ((size_t)b * NT + t) * p.V + vk;
-            const int* rowptr = p.rowptr + seg * (p.A + 1);
+            const int2 hdr = __ldg(p.sched_hdr + seg * p.nslab + slab);
+            const int4* sched = p.sched + seg * (size_t)p.A + hdr.x;
+            const int nwork = hdr.y;
             const uint4* entries = p.entries + seg * (size_t)p.seg_entries;
-            // Neighbouring anchors have lists of similar length (also when the coordinates
-            // cluster), so dealing them round-robin keeps the groups balanced.  The walk is
-            // software-pipelined: the row pointers of the anchor after next and the first chunk
-            // of the next anchor's entries are requested before the current anchor's entries are
-            // processed, so that their L2 latency hides behind that work.
-            int a = a_lo + gid;
-            int ay = y_lo + gid / AW, ax = gid % AW;
-            int beg = 0, end = 0, nbeg = 0, nend = 0;
-            if (a < a_hi) { beg = __ldg(rowptr + a); end = __ldg(rowptr + a + 1); }
-            if (a + ngroups < a_hi) { nbeg = __ldg(rowptr + a + ngroups); nend = __ldg(rowptr + a + ngroups + 1); }
+            // The work list is sorted by list length: the groups of a warp, which take neighbouring
+            // records, run loops of (nearly) equal length, and dealing the list out back and forth
+            // (0..n-1, n-1..0, ...) gives every group the same total.  The walk is software-
+            // pipelined: the record after next and the first chunk of the next record's entries
+            // are requested before the current record's entries are processed, so that their L2
+            // latency hides behind that work.
+            const int back = ngroups - 1 - gid;
+            int4 rec = make_int4(0, 0, 0, 0), nrec = rec;
+            if (gid < nwork) rec = __ldg(sched + gid);
+            if (ngroups + back < nwork) nrec = __ldg(sched + ngroups + back);
             uint4 first = make_uint4(0, 0, 0, 0);
-            if (li < CHUNK && beg + li < end) first = __ldg(entries + beg + li);
-            while (a < a_hi) {
-                int n2beg = 0, n2end = 0;
-                if (a + 2 * ngroups < a_hi) {
-                    n2beg = __ldg(rowptr + a + 2 * ngroups);
-                    n2end = __ldg(rowptr + a + 2 * ngroups + 1);
+            if (li < CHUNK && rec.y + li < rec.z) first = __ldg(entries + rec.y + li);
+            for (int round = 0; round * ngroups < nwork; ++round) {
+                int4 n2rec = make_int4(0, 0, 0, 0);
+                {
+                    const int pos2 = (round + 2) * ngroups + (round & 1 ? back : gid);
+                    if (pos2 < nwork) n2rec = __ldg(sched + pos2);
                 }
                 uint4 nfirst = make_uint4(0, 0, 0, 0);
-                if (li < CHUNK && nbeg + li < nend) nfirst = __ldg(entries + nbeg + li);
+                if (li < CHUNK && nrec.y + li < nrec.z) nfirst = __ldg(entries + nrec.y + li);
+                const int beg = rec.y, end = rec.z;
                 if (end > beg) {
                     AnchorAcc<T, D> acc;
                     acc.clear();
@@ -476,27 +547,28 @@ __global__ void __launch_bounds__(768, 1) bwd_gather_kernel(const GatherParams p
                         if (li < CHUNK) sts128(buf + (uint32_t)li * 16u, mine);
                         __syncwarp(gmask);
                         if (li < CHUNK && e0 + CHUNK + li < end) mine = __ldg(entries + e0 + CHUNK + li);
+                        auto one = [&](int i) {
+                            const uint4 ent = lds128(buf + (uint32_t)i * 16u);
+                            float2 sc;
+                            asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(sc.x), "=f"(sc.y) : "r"(sc_s + ent.y));
+                            const float wl = __uint_as_float(ent.z), wr = __uint_as_float(ent.w);
+                            acc.add(q_s + ent.x, do_s + ent.x, sc.x * wl, sc.y * wl, sc.x * wr, sc.y * wr);
+                        };
                         const int n = end - e0;
+                        if (n >= CHUNK) {
+                            // a full chunk: straight-line code, no tests between the entries
 #pragma unroll
-                        for (int i = 0; i < CHUNK; ++i) {
-                            if (i < n) {
-                                const uint4 ent = lds128(buf + (uint32_t)i * 16u);
-                                float2 sc;
-                                asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(sc.x), "=f"(sc.y) : "r"(sc_s + ent.y));
-                                const float wl = __uint_as_float(ent.z), wr = __uint_as_float(ent.w);
-                                acc.add(q_s + ent.x, do_s + ent.x, sc.x * wl, sc.y * wl, sc.x * wr, sc.y * wr);
-                            }
+                            for (int i = 0; i < CHUNK; ++i) one(i);
+                        } else {
+                            for (int i = 0; i < n; ++i) one(i);
                         }
                     }
-                    const int pix = ay * p.W + ax;  // the right pixel; the left one is pix - 1
+                    const int pix = rec.x, ax = rec.w;  // the right pixel; the left one is pix - 1
                     if (ax > 0) acc.flush_side(acc.left, dkl, dvl, pix - 1, li);
                     if (ax < p.W) acc.flush_side(acc.right, dkr, dvr, pix, li);
                 }
-                a += ngroups;
-                ay += step_y; ax += step_x;
-                if (ax >= AW) { ax -= AW; ++ay; }
-                beg = nbeg; end = nend;
-                nbeg = n2beg; nend = n2end;
+                rec = nrec;
+                nrec = n2rec;
                 first = nfirst;
             }
         }

@@ -57,7 +57,7 @@ struct GatherPlan {
     int seg_entries;         // index entries reserved per segment
     size_t index_smem;
     // byte offsets inside the workspace (after the fp32 dK/dV accumulators, if any)
-    size_t scal_bytes, entries_bytes, rowptr_bytes;
+    size_t scal_bytes, entries_bytes, sched_bytes, hdr_bytes;
 };
 GatherPlan plan_gather(const dsdpa_problem& p);
 
