@@ -120,20 +120,29 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------
 # CPU arm (the reference's path restated in C, test infrastructure)
 # --------------------------------------------------------------------------------------
+def host_threads():
+    """Host cores this process may use.  (Not OpenMP's default: torch.distributed.run sets
+    OMP_NUM_THREADS=1 for its workers, which would silently time the CPU arm on one core.)"""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except (AttributeError, OSError):
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_sample(cfg, mode, steps, warmup, target_s=15.0):
     """Times the oracle on a bounded sample of the workload: whole batch elements (all
     their heads), as many as keep one step near `target_s` seconds on this host."""
     from oracle import oracle as orc
     import ops
     inp = ops.backend.inputs
-    threads = orc.max_threads()
+    threads = host_threads()
     per_batch_qh = cfg.V * cfg.Hh * cfg.L
 
     def run(q, k, v, coords, dout):
         t0 = time.perf_counter()
-        orc.forward(q, k, v, coords, cfg.W, cfg.H, cfg.sm_scale)
+        orc.forward(q, k, v, coords, cfg.W, cfg.H, cfg.sm_scale, nthreads=threads)
         if mode == "fwdbwd":
-            orc.backward(q, k, v, coords, dout, cfg.W, cfg.H, cfg.sm_scale)
+            orc.backward(q, k, v, coords, dout, cfg.W, cfg.H, cfg.sm_scale, nthreads=threads)
         return time.perf_counter() - t0
 
     # calibration: enough batch elements to give every thread a (batch, head) slice
@@ -155,15 +164,59 @@ def cpu_sample(cfg, mode, steps, warmup, target_s=15.0):
     }
 
 
+REF_TORCH = ROOT / "baseline" / "_ref" / "ops" / "torch.py"
+
+
+def reference_torch_sample(cfg, mode, n_slices=4):
+    """Times the reference's own pure-PyTorch path, unmodified (its ops/torch.py, kept out of
+    the repository's history under baseline/_ref/), on the host cores: `n_slices` (batch, head)
+    slices of the workload, one call each (a slice is the largest piece that function can take
+    at the larger configurations: it materialises every sampled key), forward and, through
+    autograd, backward.  Slices are independent and equal-sized, so the figure extrapolates
+    linearly to the whole workload."""
+    if not REF_TORCH.exists():
+        return {"unavailable": f"{REF_TORCH.relative_to(ROOT)} is not present (it is copied from the reference by "
+                               "__graft_entry__.build() where the reference is mounted)"}
+    try:
+        import importlib.util
+        import torch
+        import ops
+        spec = importlib.util.spec_from_file_location("_reference_ops_torch", REF_TORCH)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+    except Exception as exc:  # noqa: BLE001  (e.g. einops missing on this host)
+        return {"unavailable": f"the reference's ops/torch.py does not import here: {exc!r}"}
+    threads = host_threads()
+    torch.set_num_threads(threads)
+    q, k, v, coords, dout = ops.backend.inputs.make_inputs(replace(cfg, B=1))
+    n_slices = max(1, min(n_slices, cfg.Hh))
+    t_total = 0.0
+    for h in range(n_slices):
+        qs, ks, vs, ds = (t[:, :, h:h + 1].clone() for t in (q, k, v, dout))
+        qs.requires_grad_(True), ks.requires_grad_(True), vs.requires_grad_(True)
+        t0 = time.perf_counter()
+        out = mod.deform_sdpa_torch(qs, ks, vs, coords, cfg.W, cfg.H, cfg.sm_scale)
+        if mode == "fwdbwd":
+            out.backward(ds)
+        t_total += time.perf_counter() - t0
+    qh = n_slices * cfg.V * cfg.L
+    return {"value": qh / t_total, "unit": "query-heads/sec", "cores": threads, "kind": "reference",
+            "sample": f"{n_slices} of {cfg.B * cfg.Hh} (batch, head) slices of {cfg.name}, one call of the reference's "
+                      f"deform_sdpa_torch each ({qh} query-heads), "
+                      f"{'forward+backward' if mode == 'fwdbwd' else 'forward'}, extrapolated linearly"}
+
+
 def run_reference_arm(args):
     import ops
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     cfg = ops.backend.inputs.CONFIGS[args.config]
+    # one CPU step takes about 15 s: at most three timed steps and one warm-up, whatever was asked
     steps = max(1, min(args.steps, 3))
     warm = 1 if args.warmup > 0 else 0
     r = cpu_sample(cfg, args.mode, steps, warm)
+    ref = reference_torch_sample(cfg, args.mode)
     line = {
         "impl": "reference",
         "metric": METRIC if args.mode == "fwdbwd" else METRIC_FWD,
@@ -173,6 +226,9 @@ def run_reference_arm(args):
         "config": config_dict(cfg, args, 1),
         "cpu_baseline": {"value": r["value"], "unit": r["unit"], "cores": r["cores"], "kind": r["kind"],
                          "sample": r["sample"]},
+        "cpu_baseline_reference": ref,
+        "steps_note": f"requested steps={args.steps} warmup={args.warmup}; run with steps={steps} warmup={warm} "
+                      "(a CPU step takes about 15 s)",
         "e2e": {"value": r["value"], "unit": "query-heads/sec", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -496,8 +552,9 @@ def main():
     clocks = sampler.stop() if sampler else None
     launches_all = lib.dsdpa_kernel_launches() - launches0
 
-    # did the last step's results reach rank 0?  every rank reports the sum of each of its local
-    # results; rank 0 compares with the matching slices of what it received
+    # did the last step's results reach rank 0?  every rank sends the results it computed (one more
+    # step, outside the timed region) to rank 0 over NCCL, and rank 0 compares them element by
+    # element with the matching slices of what the timed path delivered
     gather_ok = None
     if world > 1 and gather_mode != "none":
         last = step(False)
@@ -506,14 +563,20 @@ def main():
         elif side is not None:
             torch.cuda.current_stream(dev).wait_stream(side)
         barrier()
-        mine = torch.zeros(n_results, world, dtype=torch.float64, device=dev)
+        gather_ok = True
+        full = (peer.results if peer is not None else last) if rank == 0 else None
         for i, t in enumerate(last_local):
-            mine[i, rank] = t.double().sum()
-        dist.all_reduce(mine)
-        if rank == 0:
-            full = peer.results if peer is not None else last
-            got = torch.stack([torch.stack([f[s.b0:s.b1].double().sum() for s in plan]) for f in full])
-            gather_ok = bool(torch.allclose(got, mine, rtol=1e-9, atol=1e-6))
+            for src, sh in enumerate(plan):
+                shape = (sh.b1 - sh.b0, cfg.V, sh.h1 - sh.h0, cfg.L, cfg.D)
+                if rank == 0:
+                    got = t if src == 0 else torch.empty(shape, dtype=cfg.dtype, device=dev)
+                    if src != 0:
+                        dist.recv(got, src=src)
+                    want = full[i][sh.b0:sh.b1, :, sh.h0:sh.h1]
+                    gather_ok = gather_ok and bool(torch.equal(got, want))
+                elif rank == src:
+                    dist.send(t.contiguous(), dst=0)
+        barrier()
     cabi.check(lib.dsdpa_device_error(local_rank))
     # launches inside the timed region only (warm-up steps launch the same kernels)
     steps_run = args.steps + max(args.warmup, 3)
@@ -583,7 +646,7 @@ def main():
         except (KeyError, ValueError):
             pass
     peaks = measure_peaks(local_rank)
-    l2_peak, smem_peak, smem_rows_peak = peaks["l2_read"], peaks["shared"][0], peaks["shared"][1]
+    l2_peak, smem_rows_peak, l1_rows_peak = peaks["l2_read"], peaks["shared"][1], peaks["l1_row_gather"]
     qh_rank = nb * cfg.V * nh * cfg.L
     gather_b = qh_rank * cfg.gather_bytes_per_qh()
     hbm_f = qh_rank * cfg.hbm_bytes_per_qh(False)
@@ -593,40 +656,55 @@ def main():
     plan_text = cabi.describe_plan(prob)
     staged = plan_text.startswith("fwd[staged")
     gather_gbs = gather_b / (f_ms * 1e-3) / 1e9
+    # The binding roof of a row gather: the shared-memory pipe where the maps are staged (one
+    # 128-byte wavefront per cycle and SM whatever the pattern), else the L1 data path, which
+    # the same probe pattern reaches when its rows hit L1.  Both measured in this run.
+    gather_peak = smem_rows_peak if staged else l1_rows_peak
     roofline = {
         "kernel": "fwd_kernel (forward, one launch per step)",
-        "bound": "l2", "achieved": gather_gbs, "peak": l2_peak, "unit": "GB/s", "frac": gather_gbs / l2_peak,
-        # dram__bytes_read.sum + dram__bytes_write.sum of the forward kernel from the ncu capture on
-        # C5 with B=2 (118.8 MB for 200,704 query-heads; the capture's summary is committed), scaled
-        # to this launch by its query-heads: the traffic grows in proportion to the batch
-        "traffic": (118.8e6 / 200704) * qh_rank if cfg.name == "C5" else None,
-        "traffic_unit": "bytes of DRAM traffic per launch (ncu on a B=2 case, scaled by query-heads)",
+        "bound": "shared_memory" if staged else "l1",
+        "achieved": gather_gbs, "peak": gather_peak, "unit": "GB/s", "frac": gather_gbs / gather_peak,
         "algorithmic_bytes": "K/V gather bytes: query-heads x V*S keys x 8 rows x D x elem_size",
-        "peak_source": "L2 read bandwidth measured in this run (32 MB resident buffer, 128-bit loads)",
-        "note": ("K/V maps are staged in shared memory, so the gather is served above the L2 roofline; "
-                 "see shared_memory" if staged else "K/V rows gathered from L2/L1"),
-        "shared_memory": {"achieved": gather_gbs, "peak": smem_rows_peak, "unit": "GB/s",
-                          "frac": gather_gbs / smem_rows_peak,
-                          "peak_source": "shared-memory bandwidth measured in this run for the kernel's access "
-                                         "pattern (each group of 8 lanes reads an unrelated 128-byte row)",
-                          "contiguous_peak": smem_peak},
+        "peak_source": ("shared-memory read bandwidth measured in this run with the kernel's access pattern (every group "
+                        "of 8 lanes reads an unrelated 128-byte row; contiguous and 256-byte patterns measure the same)"
+                        if staged else
+                        "row gather from a 64 KB global buffer that stays in L1, measured in this run (the ceiling when "
+                        "every row hits L1; rows that miss are served by L2 at l2_read_peak)"),
+        # dram__bytes_read.sum + dram__bytes_write.sum of the forward kernel, NOT measured in this run:
+        # from the committed ncu capture of a B=2 case of this configuration, scaled to this launch
+        # by its query-heads (the traffic grows in proportion to the batch)
+        "traffic": (118.6e6 / 200704) * qh_rank if cfg.name == "C5" else None,
+        "traffic_source": "profiles/c5_b2_kernels_full_set.md (ncu, B=2 case, scaled by query-heads)" if cfg.name == "C5" else None,
+        "l2_read_peak": l2_peak,
+        "shared_patterns_GBps": {str(k_): v_ for k_, v_ in peaks["shared"].items()},
         "hbm": {"bound": "hbm", "achieved": hbm_f / (f_ms * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
                 "frac": hbm_f / (f_ms * 1e-3) / 1e9 / hbm_peak, "peak_source": f"MEASURED_PEAKS.json ({hbm_src})",
                 "algorithmic_bytes": "compulsory HBM bytes: q,k,v,out once + coords once + lse"},
         "ms_per_launch": f_ms,
     }
     if b_ms is not None:
+        # first pass: the forward's gathers again; gather pass: per sample two entries (one per map
+        # row of its footprint), each a q row, a dout row, a 16-byte entry and an 8-byte scalar pair
+        pass2_b = qh_rank * cfg.N * 2 * (2 * cfg.D * cfg.elem_size() + 24)
+        two_pass = "bwd_gather" in plan_text
+        on_chip_b = gather_b + (pass2_b if two_pass else 0)
         roofline["backward"] = {
-            "ms": b_ms, "gather_GBps": gather_b / (b_ms * 1e-3) / 1e9,
-            "scatter_GBps": qh_rank * cfg.N * 8 * cfg.D * 4 / (b_ms * 1e-3) / 1e9,
+            "ms": b_ms, "bound": roofline["bound"], "peak": gather_peak, "unit": "GB/s",
+            "achieved": on_chip_b / (b_ms * 1e-3) / 1e9, "frac": on_chip_b / (b_ms * 1e-3) / 1e9 / gather_peak,
+            "algorithmic_bytes": ("first pass: the forward's gather bytes; gather pass: query-heads x V*S x 2 entries x "
+                                  "(2 rows + 24 bytes)" if two_pass else "the forward's gather bytes (scatter form)"),
+            "kernels": "index build, first pass, gather pass: shares in profiles/bench_c5_launch_list.md",
             "hbm_GBps": hbm_b / (b_ms * 1e-3) / 1e9, "hbm_frac": hbm_b / (b_ms * 1e-3) / 1e9 / hbm_peak,
         }
+        roofline["step"] = {"frac": (gather_b + on_chip_b) / ((f_ms + b_ms) * 1e-3) / 1e9 / gather_peak,
+                            "what": "forward + backward on-chip gather bytes over their summed kernel time"}
 
-    cpu = None
+    cpu, cpu_ref = None, None
     if not args.no_cpu_baseline and world == 1:
         cpu = cpu_sample(cfg, args.mode, 1, 0)
         cpu = {"value": cpu["value"], "unit": cpu["unit"], "cores": cpu["cores"], "kind": cpu["kind"],
                "sample": cpu["sample"]}
+        cpu_ref = reference_torch_sample(cfg, args.mode)
 
     line = {
         "metric": METRIC if not fwd_only else METRIC_FWD,
@@ -639,6 +717,7 @@ def main():
         "bwd_ms": b_ms,
         "roofline": roofline,
         "cpu_baseline": cpu,
+        "cpu_baseline_reference": cpu_ref,
         "e2e": e2e,
         "gpu_launches": int(launches),
         "clocks": clocks,

@@ -8,8 +8,12 @@ from __future__ import annotations
 import ctypes
 from pathlib import Path
 
+import os
+
 _HERE = Path(__file__).resolve().parent
-LIB_PATH = _HERE / "libdeform_sdpa.so"
+# DSDPA_LIBRARY selects another build of the same library (the checked debug build,
+# libdeform_sdpa_checked.so) for a whole process.
+LIB_PATH = Path(os.environ["DSDPA_LIBRARY"]) if os.environ.get("DSDPA_LIBRARY") else _HERE / "libdeform_sdpa.so"
 
 # dsdpa_status
 OK = 0
@@ -24,6 +28,7 @@ ERR_CUDA = 8
 ERR_DEVICE_TIMEOUT = 9
 ERR_TOO_LARGE = 10
 ERR_PEER_ACCESS = 11
+ERR_DEVICE_BOUNDS = 12
 
 # dsdpa_dtype
 F32, BF16, F16 = 0, 1, 2
@@ -58,6 +63,8 @@ EXPORTS = (
     "dsdpa_last_cuda_error",
     "dsdpa_kernel_launches",
     "dsdpa_device_error",
+    "dsdpa_selftest_bounded_wait",
+    "dsdpa_build_is_checked",
     "dsdpa_describe_plan",
 )
 
@@ -127,6 +134,10 @@ def lib() -> ctypes.CDLL:
     L.dsdpa_kernel_launches.restype = ctypes.c_ulonglong
     L.dsdpa_device_error.argtypes = [ci]
     L.dsdpa_device_error.restype = ci
+    L.dsdpa_selftest_bounded_wait.argtypes = [ctypes.c_uint, ci, vp]
+    L.dsdpa_selftest_bounded_wait.restype = ci
+    L.dsdpa_build_is_checked.argtypes = []
+    L.dsdpa_build_is_checked.restype = ci
     L.dsdpa_describe_plan.argtypes = [pp, ctypes.c_char_p, ctypes.c_size_t]
     L.dsdpa_describe_plan.restype = ci
     _lib = L
@@ -146,7 +157,7 @@ def check(status: int) -> None:
     if status == ERR_CUDA:
         msg += f" (cudaError {lib().dsdpa_last_cuda_error()})"
         raise DsdpaError(status, msg)
-    if status in (ERR_DEVICE_TIMEOUT, ERR_PEER_ACCESS):
+    if status in (ERR_DEVICE_TIMEOUT, ERR_PEER_ACCESS, ERR_DEVICE_BOUNDS):
         raise DsdpaError(status, msg)
     if status == ERR_BAD_DTYPE:
         raise NotImplementedError(f"libdeform_sdpa: {msg}")

@@ -20,6 +20,21 @@ static int cuda_fail(cudaError_t e) {
     (void)cudaGetLastError();  // clear the sticky-free error state
     return DSDPA_ERR_CUDA;
 }
+// For the library's other translation units: record a failed CUDA call the same way.
+int report_cuda_failure(int cuda_error) { return cuda_fail((cudaError_t)cuda_error); }
+
+// The bounded wait on its own, for the self-test entry: one warp waits on an mbarrier nobody
+// ever completes, gives up after `polls` polls, records that and returns.
+__global__ void __launch_bounds__(32) selftest_wait_kernel(unsigned polls, int* err) {
+    __shared__ __align__(8) unsigned long long bar_storage;
+    const uint32_t bar = smem_addr(&bar_storage);
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        fence_mbar_init();
+    }
+    __syncwarp();
+    (void)mbar_wait_bounded(bar, 0u, err, polls);
+}
 
 // Sweep knobs (environment variables DSDPA_*), read once per process: the planner runs on every
 // call and must not walk the environment there.
@@ -71,13 +86,13 @@ TilePlan plan_tiles(const dsdpa_problem& p, bool backward, bool allow_priv) {
     const int force_nq = backward ? knobs().bwd_nq : knobs().fwd_nq;
 
     auto smem_need = [&](int nstage, int nw, bool priv) -> long long {
-        return (long long)nstage * 2 * map_bytes + (priv ? 2 * acc_bytes : 0) + (long long)nw * kPlanRecBytesPerWarp + 16;
+        return (long long)nstage * 2 * map_bytes + (priv ? 2 * acc_bytes : 0) + (long long)nw * kPlanRecBytesPerWarp + 32;
     };
     TilePlan best{};
     best.rounded_weights = !backward && (p.flags & DSDPA_FLAG_ROUNDED_WEIGHTS) && p.dtype != DSDPA_F32;
-    // mbarrier transaction counts hold 2^20-1 bytes; one stage is two maps
+    // mbarrier transaction counts hold 2^20-1 bytes; each map completes on a barrier of its own
     const bool can_stage = !(p.flags & DSDPA_FLAG_MAPS_FROM_L2) && smem_need(1, 4, false) <= kPlanSmemMax &&
-                           2 * map_bytes < (1ll << 20);
+                           map_bytes < (1ll << 20);
     if (can_stage) {
         const bool want_priv = backward && allow_priv && !(p.flags & DSDPA_FLAG_SCATTER_GLOBAL) &&
                                smem_need(1, 8, true) <= kPlanSmemMax;
@@ -137,7 +152,7 @@ TilePlan plan_tiles(const dsdpa_problem& p, bool backward, bool allow_priv) {
     const int cap = nw * rg.NG;
     best.tiles = (VL + cap - 1) / cap;
     best.q_per_tile = cap;
-    best.smem = (size_t)nw * kPlanRecBytesPerWarp + 16;
+    best.smem = (size_t)nw * kPlanRecBytesPerWarp + 32;
     best.ctas = (long long)p.B * p.Hh * best.tiles;
     return best;
 }
@@ -315,6 +330,7 @@ const char* dsdpa_status_string(int status) {
         case DSDPA_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel gave up";
         case DSDPA_ERR_TOO_LARGE: return "problem exceeds the maximum of this entry point";
         case DSDPA_ERR_PEER_ACCESS: return "a mirror lies in memory the launching device cannot store to";
+        case DSDPA_ERR_DEVICE_BOUNDS: return "a kernel of the checked build computed an index out of range (access skipped)";
         default: return "unknown status";
     }
 }
@@ -479,7 +495,7 @@ int dsdpa_backward_mirrored(const dsdpa_problem* p, const void* q, const void* k
         ip.B = p->B; ip.V = p->V; ip.W = p->W; ip.H = p->H; ip.L = L; ip.S = p->S;
         ip.hw = hw; ip.hh = hh; ip.tpv = gp.tpv; ip.QB = gp.QB;
         ip.rowb = p->D * dtype_size(p->dtype); ip.seg_entries = gp.seg_entries;
-        ip.A = gp.A; ip.nhist = gp.nhist; ip.nslab = gp.nslab;
+        ip.A = gp.A; ip.nhist = gp.nhist; ip.nslab = gp.nslab; ip.err = err_word;
         static bool index_attr[64] = {};
         if ((e = detail::allow_big_smem(index_build_kernel<kIndexWarpsDefault>, index_attr)) != cudaSuccess) return cuda_fail(e);
         index_build_kernel<kIndexWarpsDefault><<<(unsigned)gp.segments, kIndexWarpsDefault * 32, gp.index_smem, s>>>(ip);
@@ -607,9 +623,24 @@ int dsdpa_device_error(int device) {
     int word = 0;
     if ((e = cudaMemcpyFromSymbol(&word, g_error_word, sizeof(int))) != cudaSuccess) return cuda_fail(e);
     if (word == 0) return DSDPA_OK;
-    word = 0;
-    if ((e = cudaMemcpyToSymbol(g_error_word, &word, sizeof(int))) != cudaSuccess) return cuda_fail(e);
-    return DSDPA_ERR_DEVICE_TIMEOUT;
+    const int zero = 0;
+    if ((e = cudaMemcpyToSymbol(g_error_word, &zero, sizeof(int))) != cudaSuccess) return cuda_fail(e);
+    return word == kErrBounds ? DSDPA_ERR_DEVICE_BOUNDS : DSDPA_ERR_DEVICE_TIMEOUT;
 }
+
+int dsdpa_selftest_bounded_wait(unsigned polls, int device, void* stream) {
+    if (polls == 0 || polls > (1u << 20)) return DSDPA_ERR_BAD_SHAPE;
+    DeviceGuard guard(device);
+    if (guard.err != cudaSuccess) return cuda_fail(guard.err);
+    int* err_word = nullptr;
+    cudaError_t e = error_word_ptr(device, &err_word);
+    if (e != cudaSuccess) return cuda_fail(e);
+    selftest_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(polls, err_word);
+    if ((e = cudaGetLastError()) != cudaSuccess) return cuda_fail(e);
+    g_launches += 1;
+    return DSDPA_OK;
+}
+
+int dsdpa_build_is_checked(void) { return kBoundsCheck ? 1 : 0; }
 
 }  // extern "C"

@@ -96,8 +96,11 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
 
     if constexpr (STAGED) {
         if (threadIdx.x == 0) {
+            // per stage buffer: K's barrier, then V's
             mbar_init(bar0, 1);
             mbar_init(bar0 + 8, 1);
+            mbar_init(bar0 + 16, 1);
+            mbar_init(bar0 + 24, 1);
             fence_mbar_init();
             fence_proxy_async();
         }
@@ -107,9 +110,7 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
         }
         __syncthreads();
         if (threadIdx.x == 0) {
-            mbar_expect_tx(bar0, 2u * p.map_bytes);
-            bulk_g2s_chunked(smem0, kmaps, p.map_bytes, bar0);
-            bulk_g2s_chunked(smem0 + p.map_bytes, vmaps, p.map_bytes, bar0);
+            stage_maps(smem0, kmaps, vmaps, p.map_bytes, bar0);
         }
     }
 
@@ -144,19 +145,36 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
 
     for (int vk = 0; vk < p.V; ++vk) {
         MapReader<T, D, STAGED> kmap, vmap;
+        kmap.npix = vmap.npix = p.L;
+        kmap.err = vmap.err = p.err;
         bool ok = true;
+        // STAGED: the V map's barrier of this key view; every warp waits on it once, right before
+        // its first V row (a wait that runs out is recorded and ends the CTA at the view's end)
+        uint32_t bar_v = 0;
+        unsigned par_v = 0;
+        bool v_ready = true;
+        auto v_wait = [&]() {
+            if constexpr (STAGED) {
+                if (!v_ready) {
+                    if (!mbar_wait_bounded(bar_v, par_v, p.err)) ok = false;
+                    v_ready = true;
+                }
+            }
+        };
         if constexpr (STAGED) {
             const int stage = p.nstage == 2 ? (vk & 1) : 0;
             if (p.nstage == 2 && vk + 1 < p.V && threadIdx.x == 0) {
-                const uint32_t bar = bar0 + 8u * (uint32_t)((vk + 1) & 1);
+                const uint32_t bar = bar0 + 16u * (uint32_t)((vk + 1) & 1);
                 const uint32_t dst = smem0 + (uint32_t)((vk + 1) & 1) * 2u * p.map_bytes;
-                fence_proxy_async();
-                mbar_expect_tx(bar, 2u * p.map_bytes);
-                bulk_g2s_chunked(dst, kmaps + (size_t)(vk + 1) * map_stride_view, p.map_bytes, bar);
-                bulk_g2s_chunked(dst + p.map_bytes, vmaps + (size_t)(vk + 1) * map_stride_view, p.map_bytes, bar);
+                stage_maps(dst, kmaps + (size_t)(vk + 1) * map_stride_view, vmaps + (size_t)(vk + 1) * map_stride_view,
+                           p.map_bytes, bar);
             }
             const unsigned parity = p.nstage == 2 ? ((unsigned)(vk >> 1) & 1u) : ((unsigned)vk & 1u);
-            ok = mbar_wait_bounded(bar0 + 8u * (uint32_t)stage, parity, p.err);
+            // K first; V is waited for where it is first needed (v_wait below)
+            bar_v = bar0 + 16u * (uint32_t)stage + 8u;
+            par_v = parity;
+            v_ready = false;
+            ok = mbar_wait_bounded(bar0 + 16u * (uint32_t)stage, parity, p.err);
             ok = __all_sync(0xffffffffu, ok);
             kmap.sbase = smem0 + (uint32_t)stage * 2u * p.map_bytes;
             vmap.sbase = kmap.sbase + p.map_bytes;
@@ -242,6 +260,7 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
                             psb = __ffma2_rn(qf[e], ktb[e], psb);
                         }
                         float sa = psa.x + psa.y, sb = psb.x + psb.y, da, db;
+                        v_wait();
                         if constexpr (sizeof(T) == 2) {
                             da = corner_weighted_dot16<T, D, STAGED>(vmap, pixa, w2a, li, doraw);
                             db = corner_weighted_dot16<T, D, STAGED>(vmap, pixb, w2b, li, doraw);
@@ -303,6 +322,7 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
                         float2 kt[HP];
                         float sc, dp;        // logit in base-2 units, dout.v~
                         float ax = 0.0f, ay = 0.0f, bx = 0.0f, by = 0.0f;  // DCOORDS: d/dx, d/dy of q.k~ and dout.v~
+                        v_wait();
                         if constexpr (!DCOORDS) {
                             float2 vt[HP];
                             gather_interp<T, D, STAGED>(kmap, pix, w2, li, kt);
@@ -412,10 +432,8 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
         if constexpr (STAGED) {
             if (__syncthreads_or(ok ? 0 : 1)) return;
             if (p.nstage == 1 && vk + 1 < p.V && threadIdx.x == 0) {
-                fence_proxy_async();
-                mbar_expect_tx(bar0, 2u * p.map_bytes);
-                bulk_g2s_chunked(smem0, kmaps + (size_t)(vk + 1) * map_stride_view, p.map_bytes, bar0);
-                bulk_g2s_chunked(smem0 + p.map_bytes, vmaps + (size_t)(vk + 1) * map_stride_view, p.map_bytes, bar0);
+                stage_maps(smem0, kmaps + (size_t)(vk + 1) * map_stride_view, vmaps + (size_t)(vk + 1) * map_stride_view,
+                           p.map_bytes, bar0);
             }
             if constexpr (PRIV) {
                 // flush this key view's private dK/dV maps with vector reductions and clear them

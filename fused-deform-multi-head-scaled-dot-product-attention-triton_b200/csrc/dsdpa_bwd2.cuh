@@ -50,6 +50,7 @@ struct IndexParams {
     int A;            // anchors per map: H*(W+1)
     int nhist;        // warps that take samples, each with a histogram of its own (1..NWARPS)
     int nslab;        // slabs of map rows the gather pass splits a map into (1..kMaxSlabs)
+    int* err;         // device error word
 };
 
 constexpr int kMaxSlabs = 4;
@@ -140,7 +141,7 @@ __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexPar
             for (int r = 0; r < 2; ++r) {
                 float wl, wr;
                 const int a = entry_of(f, r, wl, wr);
-                if (a >= 0) atomicAdd(&mycnt[a], 1);
+                if (a >= 0 && in_range(a, p.A, p.err)) atomicAdd(&mycnt[a], 1);
             }
         }
     }
@@ -205,7 +206,7 @@ __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexPar
         for (int r = 0; r < 2; ++r) {
             float wl, wr;
             const int a = entry_of(f, r, wl, wr);
-            const bool valid = a >= 0;
+            const bool valid = a >= 0 && in_range(a, p.A, p.err);
             const unsigned vmask = __ballot_sync(0xffffffffu, valid);
             if (valid) {
                 const unsigned same = __match_any_sync(vmask, a);
@@ -217,7 +218,8 @@ __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexPar
                     mycnt[a] = start + __popc(same);
                 }
                 start = __shfl_sync(same, start, leader);
-                entries[start + rank] = make_uint4(roff, soff, __float_as_uint(wl), __float_as_uint(wr));
+                if (in_range(start + rank, p.seg_entries, p.err))
+                    entries[start + rank] = make_uint4(roff, soff, __float_as_uint(wl), __float_as_uint(wr));
             }
             __syncwarp();
         }
@@ -281,7 +283,7 @@ __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexPar
         if (end == beg) continue;
         const int pos = atomicAdd(&bucket[bucket_of(a, end - beg)], 1);
         const int ay = a / AW, ax = a - ay * AW;
-        sched[pos] = make_int4(ay * p.W + ax, beg, end, ax);
+        if (in_range(pos, p.A, p.err)) sched[pos] = make_int4(ay * p.W + ax, beg, end, ax);
     }
 }
 
@@ -549,6 +551,8 @@ __global__ void __launch_bounds__(768, 1) bwd_gather_kernel(const GatherParams p
                         if (li < CHUNK && e0 + CHUNK + li < end) mine = __ldg(entries + e0 + CHUNK + li);
                         auto one = [&](int i) {
                             const uint4 ent = lds128(buf + (uint32_t)i * 16u);
+                            if (!in_range(ent.x, (long long)p.QB * ROWB, p.err) || !in_range(ent.y, (long long)p.QB * p.S * 8, p.err))
+                                return;
                             float2 sc;
                             asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(sc.x), "=f"(sc.y) : "r"(sc_s + ent.y));
                             const float wl = __uint_as_float(ent.z), wr = __uint_as_float(ent.w);
@@ -564,8 +568,8 @@ __global__ void __launch_bounds__(768, 1) bwd_gather_kernel(const GatherParams p
                         }
                     }
                     const int pix = rec.x, ax = rec.w;  // the right pixel; the left one is pix - 1
-                    if (ax > 0) acc.flush_side(acc.left, dkl, dvl, pix - 1, li);
-                    if (ax < p.W) acc.flush_side(acc.right, dkr, dvr, pix, li);
+                    if (ax > 0 && in_range(pix - 1, p.L, p.err)) acc.flush_side(acc.left, dkl, dvl, pix - 1, li);
+                    if (ax < p.W && in_range(pix, p.L, p.err)) acc.flush_side(acc.right, dkr, dvr, pix, li);
                 }
                 rec = nrec;
                 nrec = n2rec;

@@ -222,10 +222,30 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, unsigned parity) {
 }
 // Bounded wait: returns false (after recording the fact) instead of spinning forever.
 // `err` points at the library's per-device error word (read back by dsdpa_device_error()).
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, unsigned parity, int* err) {
-    for (unsigned i = 0; i < kWaitLimit; ++i)
+// The error word holds the first thing a kernel had to report: kErrTimeout (a wait ran out) or,
+// in builds with -DDSDPA_BOUNDS_CHECK, kErrBounds (an index out of range; the access was skipped).
+constexpr int kErrTimeout = 1;
+constexpr int kErrBounds = 2;
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, unsigned parity, int* err, unsigned limit = kWaitLimit) {
+    for (unsigned i = 0; i < limit; ++i)
         if (mbar_try_wait(bar, parity)) return true;
-    atomicExch(err, 1);
+    atomicCAS(err, 0, kErrTimeout);
+    return false;
+}
+
+// Checked debug build (-DDSDPA_BOUNDS_CHECK): every index the kernels compute for a gathered
+// pixel row, an index entry or a shared-memory record is tested against its range before use;
+// a violation is recorded in the error word and the access is skipped (the value reads as
+// zero, a store is dropped), nothing traps.  In the normal build the test folds away.
+#ifdef DSDPA_BOUNDS_CHECK
+constexpr bool kBoundsCheck = true;
+#else
+constexpr bool kBoundsCheck = false;
+#endif
+__device__ __forceinline__ bool in_range(long long idx, long long n, int* err) {
+    if (!kBoundsCheck) return true;
+    if (idx >= 0 && idx < n) return true;
+    atomicCAS(err, 0, kErrBounds);
     return false;
 }
 // dst: shared address, src: global address, both 16-byte aligned; bytes a multiple of 16.
@@ -240,6 +260,18 @@ __device__ __forceinline__ void bulk_g2s_chunked(uint32_t dst, const char* src, 
         unsigned n = bytes - off < kPiece ? bytes - off : kPiece;
         bulk_g2s(dst + off, src + off, n, bar);
     }
+}
+
+// The K and V maps of one key view into a stage buffer ([K map][V map]) by one thread.  They
+// complete on separate barriers, K on `bar` and V on `bar + 8`: the kernels need K first (the
+// logits) and can start on it while V is still on its way.
+__device__ __forceinline__ void stage_maps(uint32_t dst, const char* ksrc, const char* vsrc, unsigned map_bytes,
+                                           uint32_t bar) {
+    fence_proxy_async();
+    mbar_expect_tx(bar, map_bytes);
+    bulk_g2s_chunked(dst, ksrc, map_bytes, bar);
+    mbar_expect_tx(bar + 8u, map_bytes);
+    bulk_g2s_chunked(dst + map_bytes, vsrc, map_bytes, bar + 8u);
 }
 
 // ---- sampling-coordinate decode --------------------------------------------------

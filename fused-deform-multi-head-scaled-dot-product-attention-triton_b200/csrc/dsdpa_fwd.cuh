@@ -70,7 +70,10 @@ struct MapReader {
     // STAGED: base is a shared-window address; else a global pointer.
     uint32_t sbase;
     const char* gbase;
+    int npix;      // pixels per map and the error word, looked at by the checked build only
+    int* err;
     __device__ __forceinline__ uint4 load(int pix, int vec) const {
+        if (!in_range(pix, npix, err) || !in_range(vec, RC::VEC, err)) return make_uint4(0, 0, 0, 0);
         if constexpr (STAGED) {
             return lds128(sbase + (uint32_t)pix * RC::ROWB + (uint32_t)vec * 16u);
         } else {
@@ -247,16 +250,17 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
 
     if constexpr (STAGED) {
         if (threadIdx.x == 0) {
+            // per stage buffer: K's barrier, then V's
             mbar_init(bar0, 1);
             mbar_init(bar0 + 8, 1);
+            mbar_init(bar0 + 16, 1);
+            mbar_init(bar0 + 24, 1);
             fence_mbar_init();
             fence_proxy_async();
         }
         __syncthreads();
         if (threadIdx.x == 0) {
-            mbar_expect_tx(bar0, 2u * p.map_bytes);
-            bulk_g2s_chunked(smem0, kmaps, p.map_bytes, bar0);
-            bulk_g2s_chunked(smem0 + p.map_bytes, vmaps, p.map_bytes, bar0);
+            stage_maps(smem0, kmaps, vmaps, p.map_bytes, bar0);
         }
     }
 
@@ -272,19 +276,36 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
 
     for (int vk = 0; vk < p.V; ++vk) {
         MapReader<T, D, STAGED> kmap, vmap;
+        kmap.npix = vmap.npix = p.L;
+        kmap.err = vmap.err = p.err;
         bool ok = true;
+        // STAGED: the V map's barrier of this key view; every warp waits on it once, right before
+        // its first V row (a wait that runs out is recorded and ends the CTA at the view's end)
+        uint32_t bar_v = 0;
+        unsigned par_v = 0;
+        bool v_ready = true;
+        auto v_wait = [&]() {
+            if constexpr (STAGED) {
+                if (!v_ready) {
+                    if (!mbar_wait_bounded(bar_v, par_v, p.err)) ok = false;
+                    v_ready = true;
+                }
+            }
+        };
         if constexpr (STAGED) {
             const int stage = p.nstage == 2 ? (vk & 1) : 0;
             if (p.nstage == 2 && vk + 1 < p.V && threadIdx.x == 0) {
-                const uint32_t bar = bar0 + 8u * (uint32_t)((vk + 1) & 1);
+                const uint32_t bar = bar0 + 16u * (uint32_t)((vk + 1) & 1);
                 const uint32_t dst = smem0 + (uint32_t)((vk + 1) & 1) * 2u * p.map_bytes;
-                fence_proxy_async();
-                mbar_expect_tx(bar, 2u * p.map_bytes);
-                bulk_g2s_chunked(dst, kmaps + (size_t)(vk + 1) * map_stride_view, p.map_bytes, bar);
-                bulk_g2s_chunked(dst + p.map_bytes, vmaps + (size_t)(vk + 1) * map_stride_view, p.map_bytes, bar);
+                stage_maps(dst, kmaps + (size_t)(vk + 1) * map_stride_view, vmaps + (size_t)(vk + 1) * map_stride_view,
+                           p.map_bytes, bar);
             }
             const unsigned parity = p.nstage == 2 ? ((unsigned)(vk >> 1) & 1u) : ((unsigned)vk & 1u);
-            ok = mbar_wait_bounded(bar0 + 8u * (uint32_t)stage, parity, p.err);
+            // K first; V is waited for where it is first needed (v_wait below)
+            bar_v = bar0 + 16u * (uint32_t)stage + 8u;
+            par_v = parity;
+            v_ready = false;
+            ok = mbar_wait_bounded(bar0 + 16u * (uint32_t)stage, parity, p.err);
             ok = __all_sync(0xffffffffu, ok);
             kmap.sbase = smem0 + (uint32_t)stage * 2u * p.map_bytes;
             vmap.sbase = kmap.sbase + p.map_bytes;
@@ -295,6 +316,10 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
             kmap.sbase = vmap.sbase = 0;
         }
 
+        // (Waiting for V only where the first V row is needed was measured slower here: the test in
+        // front of the V gathers keeps the compiler from moving their loads up into the softmax
+        // arithmetic.  The backward's first pass does wait there.)
+        v_wait();
         if (ok) {
 #pragma unroll
             for (int j = 0; j < NQ; ++j) {
@@ -422,10 +447,8 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
             // every warp is done with this buffer before it is refilled
             if (__syncthreads_or(ok ? 0 : 1)) return;
             if (p.nstage == 1 && vk + 1 < p.V && threadIdx.x == 0) {
-                fence_proxy_async();
-                mbar_expect_tx(bar0, 2u * p.map_bytes);
-                bulk_g2s_chunked(smem0, kmaps + (size_t)(vk + 1) * map_stride_view, p.map_bytes, bar0);
-                bulk_g2s_chunked(smem0 + p.map_bytes, vmaps + (size_t)(vk + 1) * map_stride_view, p.map_bytes, bar0);
+                stage_maps(smem0, kmaps + (size_t)(vk + 1) * map_stride_view, vmaps + (size_t)(vk + 1) * map_stride_view,
+                           p.map_bytes, bar0);
             }
         }
     }

@@ -23,6 +23,10 @@
 
 #include "../../include/dsdpa.h"
 
+namespace dsdpa {
+int report_cuda_failure(int cuda_error);   // dsdpa_api.cu: what dsdpa_last_cuda_error() returns
+}
+
 namespace {
 
 // The scratch itself.  In host code this name is only a handle for the runtime's symbol
@@ -32,6 +36,8 @@ namespace {
 static __device__ __align__(256) unsigned char g_static_scratch[DSDPA_STATIC_SCRATCH_BYTES];
 
 constexpr int kMaxDevices = 64;
+// (Filled without a lock: two threads that race here look the same address up twice and store
+// the same value.)
 void* g_scratch_addr[kMaxDevices] = {};
 
 // Device address of the array on `device`, looked up on first use while `device` is the
@@ -71,12 +77,11 @@ extern "C" int dsdpa_backward_static_scratch(const dsdpa_problem* p, const void*
     if (need > (size_t)DSDPA_STATIC_SCRATCH_BYTES) return DSDPA_ERR_TOO_LARGE;
     void* scratch = nullptr;
     if (need > 0) {
-        // First call on a device: symbol lookup (no allocation; the array already exists).
+        // First call on a device: symbol lookup.  The array is part of the library's device
+        // image; with CUDA's lazy module loading the driver may only place that image (and so
+        // reserve the array's memory) now, which is why this call belongs into initialisation.
         const cudaError_t e = scratch_address(device, &scratch);
-        if (e != cudaSuccess) {
-            (void)cudaGetLastError();
-            return DSDPA_ERR_CUDA;
-        }
+        if (e != cudaSuccess) return dsdpa::report_cuda_failure((int)e);
     }
     // Same kernels, same order, same checks as dsdpa_backward; only the owner of the scratch
     // differs.  The accumulators inside the scratch are zero-filled there on `stream`.

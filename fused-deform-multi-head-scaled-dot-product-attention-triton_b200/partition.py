@@ -133,6 +133,43 @@ def run_sharded(fn: Callable, q, k, v, coords, *, plan: Sequence[Shard], rank: i
     return fn(qs.contiguous(), ks.contiguous(), vs.contiguous(), cs.contiguous())
 
 
+class ShardError(RuntimeError):
+    """A shard of a sharded call failed on some rank.  ``failures`` maps rank -> message."""
+
+    def __init__(self, failures):
+        self.failures = dict(failures)
+        detail = "; ".join(f"rank {r}: {m}" for r, m in sorted(self.failures.items()))
+        super().__init__(f"sharded call failed on {len(self.failures)} rank(s): {detail}")
+
+
+def run_sharded_checked(fn: Callable, q, k, v, coords, *, plan: Sequence[Shard], rank: int, group=None,
+                        after: Optional[Callable] = None):
+    """``run_sharded`` for jobs that go on to a collective (the gather of the results): every rank
+    learns whether any shard failed BEFORE anybody enters that collective.
+
+    ``fn`` runs under try/except; ``after``, if given, runs next on the ranks whose ``fn``
+    succeeded (e.g. a check of the device's error record, which needs a synchronise and is
+    therefore optional).  The ranks then exchange one small status object.  If any rank failed,
+    every rank raises :class:`ShardError` naming the failed ranks and their messages, so that no
+    rank is left waiting in a gather for a peer that has given up; otherwise the local result is
+    returned as from ``run_sharded``."""
+    failure = None
+    local = None
+    try:
+        local = run_sharded(fn, q, k, v, coords, plan=plan, rank=rank)
+        if after is not None:
+            after(local)
+    except Exception as exc:  # noqa: BLE001  (reported to every rank below)
+        failure = f"{type(exc).__name__}: {exc}"
+    world = dist.get_world_size(group)
+    statuses = [None] * world
+    dist.all_gather_object(statuses, failure, group=group)
+    failures = {r: m for r, m in enumerate(statuses) if m is not None}
+    if failures:
+        raise ShardError(failures)
+    return local
+
+
 def _numel(shape) -> int:
     n = 1
     for d in shape:

@@ -46,7 +46,9 @@ typedef enum dsdpa_status {
     DSDPA_ERR_CUDA = 8,            /* a CUDA runtime call failed; see dsdpa_last_cuda_error() */
     DSDPA_ERR_DEVICE_TIMEOUT = 9,  /* a bounded wait inside a kernel gave up (dsdpa_device_error) */
     DSDPA_ERR_TOO_LARGE = 10,      /* beyond a stated maximum of the entry point */
-    DSDPA_ERR_PEER_ACCESS = 11     /* a mirror lies in memory the launching device cannot store to */
+    DSDPA_ERR_PEER_ACCESS = 11,    /* a mirror lies in memory the launching device cannot store to */
+    DSDPA_ERR_DEVICE_BOUNDS = 12   /* checked build only: a kernel computed an index out of range and
+                                      skipped the access (dsdpa_device_error) */
 } dsdpa_status;
 
 typedef enum dsdpa_dtype {
@@ -194,8 +196,12 @@ int dsdpa_peer_release(void* ptr, size_t offset, int device);
  *   - Same results, arguments and flags as dsdpa_backward with dcoords == NULL.
  *   - A problem whose dsdpa_backward_workspace_bytes exceeds DSDPA_STATIC_SCRATCH_BYTES is
  *     refused with DSDPA_ERR_TOO_LARGE before any work is enqueued.
- *   - The first call on a device looks up the array's device address (a symbol lookup, not
- *     an allocation).  Make that first call outside any stream capture.
+ *   - The first call on a device looks up the array's device address.  The array belongs to the
+ *     library's device image; where the CUDA runtime loads modules lazily, the driver may place
+ *     that image -- and with it reserve the DSDPA_STATIC_SCRATCH_BYTES -- only at this first
+ *     call, which can therefore fail with an out-of-memory DSDPA_ERR_CUDA on a full device.
+ *     Make that first call once per device during initialisation, outside any stream capture;
+ *     later calls touch no allocator of any kind.
  *   - All calls on a device share the one array, which keeps the previous call's contents;
  *     what has to start at zero is cleared on `stream` by every call.  Calls whose GPU work
  *     overlaps (other streams, other host threads) race on it: keep them on one stream.
@@ -221,9 +227,23 @@ int dsdpa_last_cuda_error(void);
 /*
  * Synchronises `device` and returns DSDPA_ERR_DEVICE_TIMEOUT if any kernel of this
  * library recorded that a bounded wait ran out since the last call (clearing the
- * record), DSDPA_OK otherwise.
+ * record), DSDPA_ERR_DEVICE_BOUNDS if a kernel of the checked build found an index out of
+ * range, DSDPA_OK otherwise.  A kernel that gave up returns without writing its results, and
+ * nothing else reports that: callers who need to know poll this function.
  */
 int dsdpa_device_error(int device);
+
+/*
+ * Self-test of the bounded wait every kernel's mbarrier waits go through (no counterpart in
+ * the reference, which has no device-side waits): enqueues one warp that waits on a barrier
+ * nobody completes, gives up after `polls` polls (1 .. 2^20), records the timeout and returns.
+ * dsdpa_device_error(device) then answers DSDPA_ERR_DEVICE_TIMEOUT once.  Nothing hangs or
+ * faults; the context stays usable.
+ */
+int dsdpa_selftest_bounded_wait(unsigned polls, int device, void* stream);
+
+/* 1 if this library was built with -DDSDPA_BOUNDS_CHECK (the checked debug build), else 0. */
+int dsdpa_build_is_checked(void);
 
 /*
  * How the library would run this problem: fills `text` (up to `cap` bytes, NUL

@@ -86,3 +86,46 @@ def test_two_rank_sharded_run_matches_unsharded(tmp_path, B, Hh):
     out = torch.load(result)
     assert out["equal"], "gathered sharded output differs from the unsharded one"
     assert out["shape"][0] == B and out["shape"][2] == Hh
+
+
+def _failing_worker(rank, world, port, result_dir):
+    sys.path.insert(0, str(ROOT))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import datetime
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    import ops as _ops
+    inp, prt = _ops.backend.inputs, _ops.backend.partition
+    cfg = replace(inp.CONFIGS["C2"], B=2, Hh=2, V=2, S=2, W=4, H=3)
+    q, k, v, coords, _ = inp.make_inputs(cfg)
+    plan = prt.shard_plan(cfg.B, cfg.Hh, world)
+
+    def fn(qs, ks, vs, cs):
+        if rank == 1:
+            raise ValueError("injected failure of this shard")
+        return qs.clone()
+
+    outcome = {"raised": False, "failed_ranks": None, "entered_gather": False}
+    try:
+        local = prt.run_sharded_checked(fn, q, k, v, coords, plan=plan, rank=rank)
+        outcome["entered_gather"] = True
+        prt.gather_to_root(local, plan, tuple(q.shape), root=0)
+    except prt.ShardError as err:
+        outcome["raised"] = True
+        outcome["failed_ranks"] = sorted(err.failures)
+        outcome["message"] = str(err)
+    # nobody is stuck in a collective: the group still works for everybody afterwards
+    dist.barrier()
+    torch.save(outcome, os.path.join(result_dir, f"rank{rank}.pt"))
+    dist.destroy_process_group()
+
+
+def test_a_failed_shard_reaches_every_rank_before_the_gather(tmp_path):
+    """One rank's shard raises: every rank gets a ShardError naming it, no rank enters the
+    gather, and the process group is still usable afterwards (the barrier completes)."""
+    mp.spawn(_failing_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    for rank in range(2):
+        out = torch.load(tmp_path / f"rank{rank}.pt")
+        assert out["raised"] and not out["entered_gather"]
+        assert out["failed_ranks"] == [1]
+        assert "injected failure" in out["message"] and "rank 1" in out["message"]

@@ -6,7 +6,11 @@ hand dsdpa_backward the scratch buffer it asks for.  For them the library carrie
 limit and that calls must not overlap on the GPU.  The test calls it through the C ABI twice
 in a row, with different inputs, and compares each result with what the ordinary entry
 point (scratch allocated by the caller) gives for the same inputs: the second call must not
-see anything of the first one in the shared array.
+see anything of the first one in the shared array.  Both entry points run the same kernels in
+the same fixed summation order, so the comparison is exact (bit for bit), which a leak of even
+one stale scratch word would break; the CPU oracle is compared within the path's tolerance on
+top.  The second call is also watched for allocations: neither the driver's free-memory figure
+nor torch's allocator may move across it.
 
 The file name sorts last on purpose, so that a run stopping at the first failure has
 already been through every other test.
@@ -33,7 +37,7 @@ def _inputs(seed, dtype, dev, B=1, V=3, Hh=2, W=14, H=14, D=32, S=8):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-def test_static_scratch_backward_matches_ordinary_backward_twice(dtype):
+def test_static_scratch_backward_matches_ordinary_backward_twice(dtype, oracle):
     import ops
     be = ops.backend
     cabi = be.cabi
@@ -51,16 +55,25 @@ def test_static_scratch_backward_matches_ordinary_backward_twice(dtype):
         # poisoned outputs: every element has to be written by the call
         dq, dk, dv = (torch.full_like(q, float("nan")) for _ in range(3))
         stream = torch.cuda.current_stream(dev).cuda_stream
+        torch.cuda.synchronize()
+        free_before, allocated_before = torch.cuda.mem_get_info(dev)[0], torch.cuda.memory_allocated(dev)
         st = lib.dsdpa_backward_static_scratch(ctypes.byref(prob), _ptr(q), _ptr(k), _ptr(v), _ptr(coords),
                                                _ptr(out), _ptr(lse), _ptr(dout), _ptr(dq), _ptr(dk), _ptr(dv),
                                                0, ctypes.c_void_p(stream))
         cabi.check(st)
         torch.cuda.synchronize()
+        if call > 0:
+            # (the first call on a device may make the driver place the library's image)
+            assert torch.cuda.mem_get_info(dev)[0] == free_before
+            assert torch.cuda.memory_allocated(dev) == allocated_before
         cabi.check(lib.dsdpa_device_error(0))
+        o_dq, o_dk, o_dv, _ = oracle.backward(q.float().cpu(), k.float().cpu(), v.float().cpu(), coords.cpu(),
+                                              dout.float().cpu(), W, H, sm_scale)
         tol = TOL[dtype]
-        for name, got, ref in (("dq", dq, ref_dq), ("dk", dk, ref_dk), ("dv", dv, ref_dv)):
+        for name, got, ref, orc in (("dq", dq, ref_dq, o_dq), ("dk", dk, ref_dk, o_dk), ("dv", dv, ref_dv, o_dv)):
             assert torch.isfinite(got.float()).all(), (call, name)
-            assert rel_err(got, ref) < tol, (call, name, rel_err(got, ref))
+            assert torch.equal(got, ref), (call, name, rel_err(got, ref))
+            assert rel_err(got, orc) < tol, (call, name, rel_err(got, orc))
 
 
 def test_static_scratch_backward_refuses_what_does_not_fit():
