@@ -178,12 +178,9 @@ def reference_torch_sample(cfg, mode, n_slices=4):
         return {"unavailable": f"{REF_TORCH.relative_to(ROOT)} is not present (it is copied from the reference by "
                                "__graft_entry__.build() where the reference is mounted)"}
     try:
-        import importlib.util
         import torch
         import ops
-        spec = importlib.util.spec_from_file_location("_reference_ops_torch", REF_TORCH)
-        mod = importlib.util.module_from_spec(spec)
-        spec.loader.exec_module(mod)
+        ref_fn = _load_reference_torch()
     except Exception as exc:  # noqa: BLE001  (e.g. einops missing on this host)
         return {"unavailable": f"the reference's ops/torch.py does not import here: {exc!r}"}
     threads = host_threads()
@@ -195,7 +192,7 @@ def reference_torch_sample(cfg, mode, n_slices=4):
         qs, ks, vs, ds = (t[:, :, h:h + 1].clone() for t in (q, k, v, dout))
         qs.requires_grad_(True), ks.requires_grad_(True), vs.requires_grad_(True)
         t0 = time.perf_counter()
-        out = mod.deform_sdpa_torch(qs, ks, vs, coords, cfg.W, cfg.H, cfg.sm_scale)
+        out = ref_fn(qs, ks, vs, coords, cfg.W, cfg.H, cfg.sm_scale)
         if mode == "fwdbwd":
             out.backward(ds)
         t_total += time.perf_counter() - t0
@@ -211,7 +208,7 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cfg = ops.backend.inputs.CONFIGS[args.config]
+    cfg = ops.backend.inputs.config(args.config)
     # one CPU step takes about 15 s: at most three timed steps and one warm-up, whatever was asked
     steps = max(1, min(args.steps, 3))
     warm = 1 if args.warmup > 0 else 0
@@ -251,11 +248,24 @@ def config_dict(cfg, args, world):
 # --------------------------------------------------------------------------------------
 # the reference's sweep (role of its benchmark.py)
 # --------------------------------------------------------------------------------------
+def _load_reference_torch():
+    if not REF_TORCH.exists():
+        return None
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_reference_ops_torch", REF_TORCH)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.deform_sdpa_torch
+
+
 def run_sweep():
     """Views x samples sweep with the reference's defaults (benchmark.py:16-20, 29-31: batch 2,
     32 heads, head dim 32, 18x18 map, fp32, sm_scale 0.5, V and S in {2,4,...,12}), forward and
-    backward latency (CUDA events, median of 20 after 5 warm-ups) and peak device memory of one
-    call.  One JSON line per (mode, V, S)."""
+    backward latency (CUDA events, median of 20 after at least 5 warm-ups and 50 ms) and peak
+    device memory of one call.  One JSON line per (provider, mode, V, S).  As in the reference's script
+    (benchmark.py:73-88) the second provider is the reference's own PyTorch path on the same GPU
+    (its ops/torch.py, unmodified, where baseline/_ref/ holds it): timed on the diagonal V = S and
+    on the V = 12 row, backward through autograd with the graph retained."""
     import torch
     import ops
     be = ops.backend
@@ -263,11 +273,39 @@ def run_sweep():
     B, Hh, D, W = 2, 32, 32, 18
     L = W * W
     gen = torch.Generator(device=dev).manual_seed(1)
+    ref_fn = _load_reference_torch()
+    if ref_fn is None:
+        print(json.dumps({"sweep_reference": "unavailable", "why": f"{REF_TORCH.relative_to(ROOT)} is not present"}),
+              flush=True)
+
+    def measure(fn, warm, reps):
+        # warm-up: at least `warm` calls and at least 50 ms of them (allocations of the previous
+        # point leave the GPU idle for a moment, and its clocks take a while to come back)
+        t0 = time.perf_counter()
+        n = 0
+        while n < warm or time.perf_counter() - t0 < 0.05:
+            fn()
+            n += 1
+            if n % 8 == 0:
+                torch.cuda.synchronize()
+        times = []
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record(); b.synchronize()
+            times.append(a.elapsed_time(b))
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats(dev)
+        base = torch.cuda.memory_allocated(dev)
+        fn()
+        torch.cuda.synchronize()
+        return statistics.median(times), (torch.cuda.max_memory_allocated(dev) - base) / 1e6
+
     for V in (2, 4, 6, 8, 10, 12):
         for S in (2, 4, 6, 8, 10, 12):
             q, k, v, do = (torch.randn(B, V, Hh, L, D, device=dev, generator=gen) for _ in range(4))
             coords = torch.rand(B, V, L, V, S, 2, device=dev, generator=gen)
             out, lse = be.forward_raw(q, k, v, coords, W, W, 0.5)
+            row = {"V": V, "S": S, "B": B, "heads": Hh, "D": D, "map": f"{W}x{W}", "dtype": "f32"}
 
             def fwd():
                 return be.forward_raw(q, k, v, coords, W, W, 0.5)
@@ -276,22 +314,29 @@ def run_sweep():
                 return be.backward_raw(q, k, v, coords, out, lse, do, W, W, 0.5)
 
             for mode, fn in (("fwd", fwd), ("bwd", bwd)):
-                for _ in range(5):
-                    fn()
-                times = []
-                for _ in range(20):
-                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    a.record(); fn(); b.record(); b.synchronize()
-                    times.append(a.elapsed_time(b))
-                torch.cuda.synchronize()
-                torch.cuda.reset_peak_memory_stats(dev)
-                base = torch.cuda.memory_allocated(dev)
-                fn()
-                torch.cuda.synchronize()
-                peak = torch.cuda.max_memory_allocated(dev) - base
-                print(json.dumps({"sweep": mode, "V": V, "S": S, "B": B, "heads": Hh, "D": D, "map": f"{W}x{W}",
-                                  "dtype": "f32", "latency_ms": statistics.median(times),
-                                  "peak_extra_MB": peak / 1e6}), flush=True)
+                ms, peak = measure(fn, 5, 20)
+                print(json.dumps(dict(row, sweep=mode, provider="b200", latency_ms=ms, peak_extra_MB=peak)), flush=True)
+            if ref_fn is None or not (V == S or V == 12):
+                continue
+            qr, kr, vr = (t.clone().requires_grad_(True) for t in (q, k, v))
+
+            def rfwd():
+                with torch.no_grad():
+                    return ref_fn(q, k, v, coords, W, W, 0.5)
+
+            ms, peak = measure(rfwd, 2, 5)
+            print(json.dumps(dict(row, sweep="fwd", provider="reference_torch", latency_ms=ms, peak_extra_MB=peak)),
+                  flush=True)
+            o = ref_fn(qr, kr, vr, coords, W, W, 0.5)
+
+            def rbwd():
+                o.backward(do, retain_graph=True)
+
+            ms, peak = measure(rbwd, 2, 5)
+            print(json.dumps(dict(row, sweep="bwd", provider="reference_torch", latency_ms=ms, peak_extra_MB=peak)),
+                  flush=True)
+            del o, qr, kr, vr
+            torch.cuda.empty_cache()
 
 
 def measure_peaks(dev_index):
@@ -326,7 +371,7 @@ def run_profile_case(spec):
     import ops
     be = ops.backend
     parts = spec.split(":")
-    cfg = replace(be.inputs.CONFIGS[parts[0]], B=int(parts[1]))
+    cfg = replace(be.inputs.config(parts[0]), B=int(parts[1]))
     mode = parts[2] if len(parts) > 2 else "fwd"
     flags = int(parts[3], 0) if len(parts) > 3 else 0
     dev = torch.device("cuda", 0)
@@ -384,7 +429,7 @@ def main():
         opts.is_high_priority_stream = True
         dist.init_process_group("nccl", device_id=dev, pg_options=opts)
 
-    cfg = inp.CONFIGS[args.config]
+    cfg = inp.config(args.config)
     plan = part.shard_plan(cfg.B, cfg.Hh, world)
     shard = plan[rank]
     nb = shard.b1 - shard.b0
@@ -626,9 +671,21 @@ def main():
                 pipe.run(hq, hk, hv, hc, hdo, out=h_out[0], dq=h_out[1], dk=h_out[2], dv=h_out[3])
         e_total = timed(estep, max(2, min(args.steps, 5)), 3)
         e_ms = e_total / max(2, min(args.steps, 5))
+        # what the copies of one more step (outside the timed region) sustained on every rank
+        pipe.time_transfers = True
+        estep(False)
+        torch.cuda.synchronize()
+        rates = pipe.transfer_rates()
+        per_rank = [None] * world
+        if world > 1:
+            dist.all_gather_object(per_rank, rates)
+        else:
+            per_rank = [rates]
         # bytes are per rank; the job moves world times as much
         e2e = {"value": cfg.query_heads / (e_ms * 1e-3), "unit": "query-heads/sec", "ms_per_step": e_ms,
-               "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world}
+               "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
+               "chunks": [b1 - b0 for b0, b1 in be.host.chunk_schedule(nb, pipe.chunk)],
+               "transfers_per_rank": per_rank}
         del hq, hk, hv, hdo, hc, h_out
 
     if rank != 0:

@@ -66,6 +66,10 @@ class HostPipeline:
         self.s_in = torch.cuda.Stream(self.device)
         self.s_comp = torch.cuda.Stream(self.device)
         self.s_out = torch.cuda.Stream(self.device)
+        # With ``time_transfers = True`` every run brackets its copies in and its copies out with
+        # timing events; ``transfer_rates()`` then gives the bandwidth they reached.
+        self.time_transfers = False
+        self._marks = None
 
     def _to_device(self, hosts: Sequence[Optional[torch.Tensor]], b0: int, b1: int):
         out = []
@@ -98,6 +102,13 @@ class HostPipeline:
         start.record(cur)
         for s in (self.s_in, self.s_comp, self.s_out):
             s.wait_event(start)
+        marks = None
+        if self.time_transfers:
+            marks = {n: torch.cuda.Event(enable_timing=True) for n in ("in0", "in1", "out0", "out1")}
+            marks["in0"].record(self.s_in)
+            marks["bytes_in"] = sum(t.numel() * t.element_size() for t in (q, k, v, coords, dout) if t is not None)
+            marks["bytes_out"] = sum(t.numel() * t.element_size() for n, t in results.items() if not direct[n])
+            first_out = True
         for b0, b1 in chunk_schedule(B, self.chunk):
             with torch.cuda.stream(self.s_in):
                 d_q, d_k, d_v, d_c = self._to_device((q, k, v, coords), b0, b1)
@@ -127,10 +138,32 @@ class HostPipeline:
             with torch.cuda.stream(self.s_out):
                 for event, host, dev_t in copies:
                     self.s_out.wait_event(event)
+                    if marks is not None and first_out:
+                        marks["out0"].record(self.s_out)
+                        first_out = False
                     dev_t.record_stream(self.s_out)
                     host[b0:b1].copy_(dev_t, non_blocking=True)
+        if marks is not None:
+            marks["in1"].record(self.s_in)
+            marks["out1"].record(self.s_out)
+            self._marks = marks
         for s in (self.s_comp, self.s_out):
             end = torch.cuda.Event()
             end.record(s)
             cur.wait_event(end)
         return out
+
+    def transfer_rates(self):
+        """Of the last run with ``time_transfers`` set (synchronise first): bytes copied in / out
+        over the time from the start of the first such copy to the end of the last one, in GB/s.
+        The copies out wait for the kernels that produce their data, so that window also holds
+        those waits: the figure is what the pipeline sustained, not the link's peak."""
+        m = self._marks
+        if m is None:
+            return None
+        t_in = m["in0"].elapsed_time(m["in1"]) * 1e-3
+        rates = {"h2d_GBps": m["bytes_in"] / t_in / 1e9 if t_in > 0 else None, "h2d_window_ms": t_in * 1e3}
+        if m["bytes_out"]:
+            t_out = m["out0"].elapsed_time(m["out1"]) * 1e-3
+            rates.update(d2h_GBps=m["bytes_out"] / t_out / 1e9 if t_out > 0 else None, d2h_window_ms=t_out * 1e3)
+        return rates

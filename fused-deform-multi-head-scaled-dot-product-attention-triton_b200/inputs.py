@@ -67,6 +67,23 @@ CONFIGS = {
                  coords="uniform"),
 }
 
+# Not benchmark configurations: the quick-start shape in the other storage types and head
+# dimensions the reference accepts (ops/triton.py:367-375, 386), to put a number on those paths.
+EXTRA_CONFIGS = {
+    "X_f16_d128": Config("X_f16_d128", B=2, V=8, S=32, Hh=16, D=128, W=14, H=14, sm_scale=128 ** -0.5,
+                         dtype=torch.float16, coords="uniform"),
+    "X_f32_d256": Config("X_f32_d256", B=2, V=8, S=32, Hh=16, D=256, W=14, H=14, sm_scale=256 ** -0.5,
+                         dtype=torch.float32, coords="uniform"),
+    "X_bf16_d16": Config("X_bf16_d16", B=2, V=8, S=32, Hh=16, D=16, W=14, H=14, sm_scale=0.25,
+                         dtype=torch.bfloat16, coords="uniform"),
+}
+
+
+def config(name: str) -> Config:
+    """A benchmark configuration (C1..C5) or one of EXTRA_CONFIGS by name."""
+    return CONFIGS[name] if name in CONFIGS else EXTRA_CONFIGS[name]
+
+
 SEED0 = 20240607
 
 
