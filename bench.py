@@ -45,6 +45,8 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="C5")
     ap.add_argument("--mode", default="fwdbwd", choices=["fwdbwd", "fwd"])
+    ap.add_argument("--flags", type=lambda x: int(x, 0), default=0,
+                    help="DSDPA_FLAG_* bits for every call (e.g. 0x10, rounded weights; 0x8, the scatter backward)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--sweep", action="store_true",
@@ -507,14 +509,15 @@ def main():
     def step(record):
         e0, e1, e2 = ev(), ev(), ev()
         e0.record()
-        out, lse = be.forward_raw(q, k, v, coords, cfg.W, cfg.H, cfg.sm_scale,
+        out, lse = be.forward_raw(q, k, v, coords, cfg.W, cfg.H, cfg.sm_scale, flags=args.flags,
                                   out_mirror=views[0] if views and fwd_only else None)
         e1.record()
         res = [out]
         if not fwd_only:
             # (with mirrors the backward's first pass, which reads out anyway, sends it along)
             mir = dict(zip(("out", "dq", "dk", "dv"), views)) if views else None
-            dq, dk, dv, _ = be.backward_raw(q, k, v, coords, out, lse, dout, cfg.W, cfg.H, cfg.sm_scale, mirrors=mir)
+            dq, dk, dv, _ = be.backward_raw(q, k, v, coords, out, lse, dout, cfg.W, cfg.H, cfg.sm_scale,
+                                            flags=args.flags, mirrors=mir)
             e2.record()
             res += [dq, dk, dv]
         last_local[:] = res
@@ -636,7 +639,7 @@ def main():
     fwd_value = None
     if not fwd_only:
         def fstep(_record):
-            out, _lse = be.forward_raw(q, k, v, coords, cfg.W, cfg.H, cfg.sm_scale,
+            out, _lse = be.forward_raw(q, k, v, coords, cfg.W, cfg.H, cfg.sm_scale, flags=args.flags,
                                        out_mirror=views[0] if views else None)
             if views is not None:
                 return out
@@ -709,7 +712,7 @@ def main():
     hbm_f = qh_rank * cfg.hbm_bytes_per_qh(False)
     hbm_b = qh_rank * cfg.hbm_bytes_per_qh(True)
     dt = {torch.float32: cabi.F32, torch.bfloat16: cabi.BF16, torch.float16: cabi.F16}[cfg.dtype]
-    prob = cabi.Problem(nb, cfg.V, nh, cfg.W, cfg.H, cfg.D, cfg.S, cfg.sm_scale, dt, 0)
+    prob = cabi.Problem(nb, cfg.V, nh, cfg.W, cfg.H, cfg.D, cfg.S, cfg.sm_scale, dt, args.flags)
     plan_text = cabi.describe_plan(prob)
     staged = plan_text.startswith("fwd[staged")
     gather_gbs = gather_b / (f_ms * 1e-3) / 1e9
@@ -779,6 +782,7 @@ def main():
         "gpu_launches": int(launches),
         "clocks": clocks,
         "plan": plan_text,
+        "flags": args.flags,
         "gather": (None if world == 1 else
                    {"how": {"mirror": "the kernels store each result row also into rank 0's tensors over NVLink "
                                       "(CUDA IPC mapping)",

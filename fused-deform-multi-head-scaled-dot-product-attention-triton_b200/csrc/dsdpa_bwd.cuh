@@ -148,8 +148,8 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
         kmap.npix = vmap.npix = p.L;
         kmap.err = vmap.err = p.err;
         bool ok = true;
-        // STAGED: the V map's barrier of this key view; every warp waits on it once, right before
-        // its first V row (a wait that runs out is recorded and ends the CTA at the view's end)
+        // STAGED: the V map's barrier of this key view, waited for right behind K's (a wait that
+        // runs out is recorded and ends the CTA at the view's end)
         uint32_t bar_v = 0;
         unsigned par_v = 0;
         bool v_ready = true;
@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
                            p.map_bytes, bar);
             }
             const unsigned parity = p.nstage == 2 ? ((unsigned)(vk >> 1) & 1u) : ((unsigned)vk & 1u);
-            // K first; V is waited for where it is first needed (v_wait below)
+            // K first, then V (v_wait below)
             bar_v = bar0 + 16u * (uint32_t)stage + 8u;
             par_v = parity;
             v_ready = false;
@@ -187,6 +187,8 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
         float* dkmap = dkmaps + (size_t)vk * acc_stride_view;
         float* dvmap = dvmaps + (size_t)vk * acc_stride_view;
 
+        // (as in the forward: waiting for V only in front of the first V row was measured slower)
+        v_wait();
         if (ok) {
 #pragma unroll
             for (int j = 0; j < NQ; ++j) {
@@ -260,7 +262,6 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
                             psb = __ffma2_rn(qf[e], ktb[e], psb);
                         }
                         float sa = psa.x + psa.y, sb = psb.x + psb.y, da, db;
-                        v_wait();
                         if constexpr (sizeof(T) == 2) {
                             da = corner_weighted_dot16<T, D, STAGED>(vmap, pixa, w2a, li, doraw);
                             db = corner_weighted_dot16<T, D, STAGED>(vmap, pixb, w2b, li, doraw);
@@ -322,7 +323,6 @@ __global__ void __launch_bounds__(MAXT, MINB) bwd_scatter_kernel(const BwdParams
                         float2 kt[HP];
                         float sc, dp;        // logit in base-2 units, dout.v~
                         float ax = 0.0f, ay = 0.0f, bx = 0.0f, by = 0.0f;  // DCOORDS: d/dx, d/dy of q.k~ and dout.v~
-                        v_wait();
                         if constexpr (!DCOORDS) {
                             float2 vt[HP];
                             gather_interp<T, D, STAGED>(kmap, pix, w2, li, kt);

@@ -263,8 +263,8 @@ __device__ __forceinline__ void bulk_g2s_chunked(uint32_t dst, const char* src, 
 }
 
 // The K and V maps of one key view into a stage buffer ([K map][V map]) by one thread.  They
-// complete on separate barriers, K on `bar` and V on `bar + 8`: the kernels need K first (the
-// logits) and can start on it while V is still on its way.
+// complete on separate barriers, K on `bar` and V on `bar + 8` (an mbarrier counts up to 2^20-1
+// bytes per phase, one map each keeps larger maps stageable).
 __device__ __forceinline__ void stage_maps(uint32_t dst, const char* ksrc, const char* vsrc, unsigned map_bytes,
                                            uint32_t bar) {
     fence_proxy_async();

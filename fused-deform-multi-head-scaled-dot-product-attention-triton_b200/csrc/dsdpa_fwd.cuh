@@ -279,8 +279,8 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
         kmap.npix = vmap.npix = p.L;
         kmap.err = vmap.err = p.err;
         bool ok = true;
-        // STAGED: the V map's barrier of this key view; every warp waits on it once, right before
-        // its first V row (a wait that runs out is recorded and ends the CTA at the view's end)
+        // STAGED: the V map's barrier of this key view, waited for right behind K's (a wait that
+        // runs out is recorded and ends the CTA at the view's end)
         uint32_t bar_v = 0;
         unsigned par_v = 0;
         bool v_ready = true;
@@ -301,7 +301,7 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
                            p.map_bytes, bar);
             }
             const unsigned parity = p.nstage == 2 ? ((unsigned)(vk >> 1) & 1u) : ((unsigned)vk & 1u);
-            // K first; V is waited for where it is first needed (v_wait below)
+            // K first, then V (v_wait below)
             bar_v = bar0 + 16u * (uint32_t)stage + 8u;
             par_v = parity;
             v_ready = false;
@@ -316,9 +316,9 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
             kmap.sbase = vmap.sbase = 0;
         }
 
-        // (Waiting for V only where the first V row is needed was measured slower here: the test in
-        // front of the V gathers keeps the compiler from moving their loads up into the softmax
-        // arithmetic.  The backward's first pass does wait there.)
+        // (Waiting for V only where the first V row is needed was measured slower, here and in the
+        // backward's first pass: the test in front of the V gathers keeps the compiler from moving
+        // their loads up into the arithmetic before them.)
         v_wait();
         if (ok) {
 #pragma unroll
