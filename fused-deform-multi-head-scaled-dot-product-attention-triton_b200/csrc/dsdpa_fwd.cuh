@@ -33,6 +33,8 @@
 
 namespace dsdpa {
 
+template <int N> struct IntC { static constexpr int value = N; };   // a compile-time int as an argument
+
 struct FwdParams {
     const void* q;
     const void* k;
@@ -221,7 +223,11 @@ __device__ __forceinline__ void corner_dots(const MapReader<T, D, STAGED>& map, 
     }
 }
 
-template <typename T, int D, int NQ, bool STAGED, int MAXT, int MINB, bool RW = false>
+// TAILS: the sample count per key view is not a multiple of the batch size (or a group's chunk of
+// samples is smaller than a batch): what is left after the whole batches is taken in twos and
+// ones.  Without it every chunk is whole batches and that code is left out, which keeps the
+// common case's inner loop as tight as the compiler makes it on its own.
+template <typename T, int D, int NQ, bool STAGED, int MAXT, int MINB, bool RW = false, bool TAILS = false>
 __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
     static_assert(!RW || sizeof(T) == 2, "rounded weights are a 16-bit storage option");
     using RC = RowCfg<T, D>;
@@ -355,14 +361,16 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
                     const int cnt = min(G, p.S - s0);
                     // U samples per iteration: their gathers and dot-product reductions overlap, and
                     // the running maximum is updated once for the batch
-                    constexpr int U = STAGED ? DSDPA_FWD_UNROLL : DSDPA_FWD_UNROLL_L2;
-                    for (int i = 0; i < cnt; i += U) {
+                    constexpr int UMAX = STAGED ? DSDPA_FWD_UNROLL : DSDPA_FWD_UNROLL_L2;
+                    // samples i .. i+U-1 of the chunk.  TAILS: all of them exist; else samples past the
+                    // chunk's end repeat its last one and are masked out of the softmax
+                    auto batch = [&](int i, auto u_const) {
+                        constexpr int U = decltype(u_const)::value;
                         float2 w2[U][4];
                         int pix[U][4];
 #pragma unroll
                         for (int u = 0; u < U; ++u) {
-                            const int iu = min(i + u, cnt - 1);     // a repeat of the last sample is ignored below
-                            const uint32_t r = rec_slot<G, NG>(iu, g) * 16u;
+                            const uint32_t r = rec_slot<G, NG>(TAILS ? i + u : min(i + u, cnt - 1), g) * 16u;
                             const uint4 wr = lds128(rec_w + r), pr = lds128(rec_p + r);
                             w2[u][0] = make_float2(__uint_as_float(wr.x), __uint_as_float(wr.x));
                             w2[u][1] = make_float2(__uint_as_float(wr.y), __uint_as_float(wr.y));
@@ -395,7 +403,7 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
                         float smax = sc[0];
 #pragma unroll
                         for (int u = 1; u < U; ++u) {
-                            if (i + u >= cnt) sc[u] = -INFINITY;    // same for the whole warp
+                            if (!TAILS && i + u >= cnt) sc[u] = -INFINITY;    // same for the whole warp
                             smax = fmaxf(smax, sc[u]);
                         }
                         if (smax > m) {
@@ -435,6 +443,19 @@ __global__ void __launch_bounds__(MAXT, MINB) fwd_kernel(const FwdParams p) {
 #pragma unroll
                                 for (int e = 0; e < HP; ++e) acc[j][e] = __ffma2_rn(p2, vt[e], acc[j][e]);
                             }
+                        }
+                    };
+                    if constexpr (!TAILS) {
+                        for (int i = 0; i < cnt; i += UMAX) batch(i, IntC<UMAX>{});
+                    } else {
+                        // whole batches, then what is left in twos and ones: no padded work
+                        int i = 0;
+                        for (; i + UMAX <= cnt; i += UMAX) batch(i, IntC<UMAX>{});
+                        if constexpr (UMAX > 2) {
+                            for (; i + 2 <= cnt; i += 2) batch(i, IntC<2>{});
+                        }
+                        if constexpr (UMAX > 1) {
+                            for (; i < cnt; ++i) batch(i, IntC<1>{});
                         }
                     }
                     __syncwarp();

@@ -46,15 +46,27 @@ inline cudaError_t allow_big_smem(K kern, bool (&done)[64]) {
     return e;
 }
 
-template <typename T, int D, int NQ, bool STAGED, bool RW = false, int MAXT = (STAGED ? kStagedMaxThreads : kL2MaxThreads)>
-inline cudaError_t fwd_one(const FwdParams& p, const TilePlan& plan, cudaStream_t stream) {
-    auto kern = fwd_kernel<T, D, NQ, STAGED, MAXT, STAGED ? 1 : kL2MinBlocks, RW>;
+template <typename T, int D, int NQ, bool STAGED, bool RW, bool TAILS, int MAXT = (STAGED ? kStagedMaxThreads : kL2MaxThreads)>
+inline cudaError_t fwd_launch(const FwdParams& p, const TilePlan& plan, cudaStream_t stream) {
+    auto kern = fwd_kernel<T, D, NQ, STAGED, MAXT, STAGED ? 1 : kL2MinBlocks, RW, TAILS>;
     if (plan.nw * 32 > MAXT) return cudaErrorInvalidValue;
     static bool done[64] = {};  // a benign race at worst repeats the attribute call
     cudaError_t e = allow_big_smem(kern, done);
     if (e != cudaSuccess) return e;
     kern<<<(unsigned)plan.ctas, plan.nw * 32, plan.smem, stream>>>(p);
     return cudaGetLastError();
+}
+
+// Samples come to a group in chunks of G (its lane count) and are taken UMAX at a time: when
+// every chunk is whole batches the kernel without the tail code runs (it pads an incomplete
+// batch instead, which then never happens).
+template <typename T, int D, int NQ, bool STAGED, bool RW = false>
+inline cudaError_t fwd_one(const FwdParams& p, const TilePlan& plan, cudaStream_t stream) {
+    constexpr int G = RowCfg<T, D>::G;
+    constexpr int UMAX = STAGED ? DSDPA_FWD_UNROLL : DSDPA_FWD_UNROLL_L2;
+    const bool whole = G % UMAX == 0 && p.S % UMAX == 0;
+    return whole ? fwd_launch<T, D, NQ, STAGED, RW, false>(p, plan, stream)
+                 : fwd_launch<T, D, NQ, STAGED, RW, true>(p, plan, stream);
 }
 
 template <typename T, int D>
