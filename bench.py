@@ -665,7 +665,9 @@ def main():
 
         # the operator's front end for host tensors: chunks of batch elements on three streams
         # (copy in, compute, copy out); every byte still crosses PCIe inside the timed region
-        pipe = be.HostPipeline(dev, cfg.W, cfg.H, cfg.sm_scale, chunk=max(1, min(int(os.environ.get("BENCH_E2E_CHUNK", "8")), nb)))
+        sizes = [int(x) for x in os.environ["BENCH_E2E_SIZES"].split(",")] if os.environ.get("BENCH_E2E_SIZES") else None
+        pipe = be.HostPipeline(dev, cfg.W, cfg.H, cfg.sm_scale, sizes=sizes,
+                               chunk=max(1, min(int(os.environ.get("BENCH_E2E_CHUNK", "8")), nb)))
 
         def estep(_record):
             if fwd_only:
@@ -687,7 +689,7 @@ def main():
         # bytes are per rank; the job moves world times as much
         e2e = {"value": cfg.query_heads / (e_ms * 1e-3), "unit": "query-heads/sec", "ms_per_step": e_ms,
                "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
-               "chunks": [b1 - b0 for b0, b1 in be.host.chunk_schedule(nb, pipe.chunk)],
+               "chunks": pipe.sizes or [b1 - b0 for b0, b1 in be.host.chunk_schedule(nb, pipe.chunk)],
                "transfers_per_rank": per_rank}
         del hq, hk, hv, hdo, hc, h_out
 

@@ -57,10 +57,11 @@ class HostPipeline:
     """
 
     def __init__(self, device, W: int, H: int, sm_scale: float, chunk: int = 8, flags: Optional[int] = None,
-                 direct_results: bool = False):
+                 direct_results: bool = False, sizes: Optional[Sequence[int]] = None):
         self.device = torch.device(device)
         self.W, self.H, self.sm_scale = int(W), int(H), float(sm_scale)
         self.chunk = max(1, int(chunk))
+        self.sizes = list(sizes) if sizes else None   # explicit chunk sizes (must add up to the batch)
         self.flags = flags
         self.direct_results = bool(direct_results)
         self.s_in = torch.cuda.Stream(self.device)
@@ -109,7 +110,14 @@ class HostPipeline:
             marks["bytes_in"] = sum(t.numel() * t.element_size() for t in (q, k, v, coords, dout) if t is not None)
             marks["bytes_out"] = sum(t.numel() * t.element_size() for n, t in results.items() if not direct[n])
             first_out = True
-        for b0, b1 in chunk_schedule(B, self.chunk):
+        if self.sizes is not None:
+            if sum(self.sizes) != B or min(self.sizes) < 1:
+                raise ValueError(f"chunk sizes {self.sizes} do not cover a batch of {B}")
+            bounds = [sum(self.sizes[:i]) for i in range(len(self.sizes) + 1)]
+            schedule = list(zip(bounds[:-1], bounds[1:]))
+        else:
+            schedule = chunk_schedule(B, self.chunk)
+        for b0, b1 in schedule:
             with torch.cuda.stream(self.s_in):
                 d_q, d_k, d_v, d_c = self._to_device((q, k, v, coords), b0, b1)
                 ready_fwd = torch.cuda.Event()

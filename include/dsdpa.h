@@ -59,7 +59,10 @@ typedef enum dsdpa_dtype {
 
 /* Flags (OR-ed).  0 selects the default path for the shape. */
 #define DSDPA_FLAG_MAPS_FROM_L2    0x1u /* never stage K/V maps in shared memory: gather with read-only loads */
-#define DSDPA_FLAG_DETERMINISTIC   0x2u /* backward: two-pass dK/dV with a fixed summation order */
+#define DSDPA_FLAG_DETERMINISTIC   0x2u /* backward: two-pass dK/dV with a fixed summation order: dq, dk, dv
+                                           are bit-reproducible run to run (the default form where the
+                                           shape allows it; the flag refuses the scatter flags).  dcoords,
+                                           summed over the heads with floating-point reductions, is not */
 #define DSDPA_FLAG_SCATTER_GLOBAL  0x4u /* backward scatter: reductions straight to global memory,
                                            no shared-memory privatised accumulation */
 #define DSDPA_FLAG_SCATTER         0x8u /* backward: force the one-kernel scatter form */
@@ -93,7 +96,12 @@ int dsdpa_forward(const dsdpa_problem* p,
 
 /*
  * Bytes of scratch dsdpa_backward needs for this problem (0 is possible).
- * Depends on the shape, dtype and flags only.
+ * Depends on the shape, dtype and flags only.  Two-pass form: fp32 accumulator maps (four times
+ * the element count of dk for 16-bit storage, twice for fp32), 8 bytes per (query-head, sample)
+ * of first-pass scalars and the sorted index (about 32 bytes per (query, sample), shared by the
+ * heads); roughly 3.5x the bytes of q, k, v, out, dout, dq, dk, dv together at the scaling
+ * configuration.  The reference allocates its fp32 dK/dV accumulators per call as well
+ * (ops/triton.py:427-430).
  */
 size_t dsdpa_backward_workspace_bytes(const dsdpa_problem* p);
 
