@@ -51,7 +51,7 @@ static const Knobs& knobs() {
     static const Knobs k = {
         env_int("DSDPA_FWD_NW", 0), env_int("DSDPA_FWD_NQ", 0), env_int("DSDPA_BWD_NW", 0), env_int("DSDPA_BWD_NQ", 0),
         env_int("DSDPA_GATHER_SMEM_KB", 224), env_int("DSDPA_INDEX_SMEM_KB", 112), env_int("DSDPA_GATHER_QB", 0),
-        env_int("DSDPA_GATHER_THREADS", 768), env_int("DSDPA_GATHER_NSLAB", 0), env_int("DSDPA_BWD_TWO_PASS", 1),
+        env_int("DSDPA_GATHER_THREADS", 0), env_int("DSDPA_GATHER_NSLAB", 0), env_int("DSDPA_BWD_TWO_PASS", 1),
     };
     return k;
 }
@@ -164,8 +164,8 @@ GatherPlan plan_gather(const dsdpa_problem& p) {
     const long long rowb = (long long)p.D * dtype_size(p.dtype);
     const long long per_query = 2 * rowb + (long long)p.S * 8;
     g.gather_threads = knobs().gather_threads;
-    if (g.gather_threads < 32 || g.gather_threads > kGatherMaxThreads || g.gather_threads % 32)
-        g.gather_threads = kGatherMaxThreads;
+    if (g.gather_threads < 32 || g.gather_threads > gather_max_threads(p.dtype) || g.gather_threads % 32)
+        g.gather_threads = gather_max_threads(p.dtype);
     // every group of lanes keeps a small ring of index entries in shared memory
     const RowGeom rg = row_geom(p.D, p.dtype);
     const long long chunk = rg.G < 8 ? rg.G : 8;

@@ -34,6 +34,7 @@
 #pragma once
 
 #include "dsdpa_common.cuh"
+#include "dsdpa_plan.h"
 
 namespace dsdpa {
 
@@ -451,7 +452,8 @@ struct GatherRing {
 // the tile's scalars ([QB, S] float2), all three filled by bulk copies; then the mbarrier and
 // the groups' entry rings.
 template <typename T, int D>
-__global__ void __launch_bounds__(768, 1) bwd_gather_kernel(const GatherParams p) {
+__global__ void __launch_bounds__(sizeof(T) == 2 ? kGatherThreadsNarrow : kGatherThreadsFp32, 1)
+bwd_gather_kernel(const GatherParams p) {
     using RC = RowCfg<T, D>;
     constexpr int G = RC::G, NG = RC::NG, ROWB = RC::ROWB;
     constexpr int CHUNK = GatherRing<G>::CHUNK;
