@@ -118,6 +118,33 @@ def test_plans_of_the_five_configurations():
     assert text.startswith("fwd[l2")
 
 
+def test_backward_form_by_map_size_and_flags():
+    """The two-pass form (and with it the coordinate gradient) runs for maps up to the index
+    builder's limit -- with fewer histograms for large ones -- and gives way to the scatter form
+    beyond it or under the scatter flags; the gather pass's grid is units x slabs."""
+    lib = cabi.lib()
+
+    def plan(W, H, flags=0, dtype=cabi.F32, D=16):
+        prob = cabi.Problem(1, 2, 1, W, H, D, 2, 0.25, dtype, flags)
+        return cabi.describe_plan(prob), lib.dsdpa_backward_supports_dcoords(ctypes.byref(prob))
+
+    for W, H in ((14, 14), (100, 80), (160, 160)):
+        text, dc = plan(W, H)
+        assert "bwd_pass_a[" in text and "bwd_gather[" in text and dc == 1, (W, H, text)
+    text, dc = plan(250, 240)
+    assert "bwd_scatter[" in text and "bwd_gather" not in text and dc == 0
+    text, dc = plan(14, 14, cabi.FLAG_SCATTER)
+    assert "bwd_scatter[" in text and dc == 0
+    assert lib.dsdpa_backward_supports_dcoords(None) == 0
+    m = re.search(r"bwd_gather\[tpv=(\d+) QB=(\d+) nslab=(\d+) ctas=(\d+) smem=(\d+) segments=(\d+)\]", plan(14, 14)[0])
+    tpv, qb, nslab, ctas, smem, segments = map(int, m.groups())
+    assert tpv * qb >= 14 * 14 and ctas == 1 * 1 * 2 * nslab and smem <= 232448 and segments == 1 * 2 * tpv * 2
+    # 16-bit storage runs the gather pass with fewer threads than fp32 storage: its plan leaves room
+    c5 = be.inputs.CONFIGS["C5"]
+    t5 = cabi.describe_plan(cabi.Problem(c5.B, c5.V, c5.Hh, c5.W, c5.H, c5.D, c5.S, c5.sm_scale, cabi.BF16, 0))
+    assert re.search(r"bwd_gather\[tpv=2 QB=392 ", t5), t5
+
+
 def test_rounded_weights_flag_is_a_16_bit_forward_option():
     c5 = be.inputs.CONFIGS["C5"]
     args = (c5.B, c5.V, c5.Hh, c5.W, c5.H, c5.D, c5.S, c5.sm_scale)
