@@ -204,6 +204,27 @@ def test_host_pipeline_equals_one_shot_call(backend, results):
     assert torch.equal(dq, ref[2].cpu()) and torch.equal(dk, ref[3].cpu()) and torch.equal(dv, ref[4].cpu())
 
 
+def test_host_pipeline_with_given_chunk_sizes(backend):
+    """Explicit chunk sizes give the same bits; sizes that do not cover the batch are refused; the
+    transfer rates of a timed run are reported."""
+    from dataclasses import replace
+    cfg = replace(backend.inputs.CONFIGS["C2"], B=5)
+    q, k, v, coords, dout = backend.inputs.make_inputs(cfg, pin=True)
+    dev = torch.device("cuda", 0)
+    ref = _run(backend, (q, k, v, coords, dout), 0, cfg.dtype, cfg.W, cfg.H, cfg.sm_scale)
+    out, dq, dk, dv = (torch.zeros_like(q).pin_memory() for _ in range(4))
+    pipe = backend.HostPipeline(dev, cfg.W, cfg.H, cfg.sm_scale, sizes=[2, 3])
+    pipe.time_transfers = True
+    pipe.run(q, k, v, coords, dout, out=out, dq=dq, dk=dk, dv=dv)
+    torch.cuda.synchronize()
+    assert torch.equal(out, ref[0].cpu()) and torch.equal(dk, ref[3].cpu()) and torch.equal(dv, ref[4].cpu())
+    rates = pipe.transfer_rates()
+    assert rates["h2d_GBps"] > 0 and rates["d2h_GBps"] > 0
+    with pytest.raises(ValueError):
+        backend.HostPipeline(dev, cfg.W, cfg.H, cfg.sm_scale, sizes=[2, 2]).run(q, k, v, coords, dout, out=out, dq=dq,
+                                                                               dk=dk, dv=dv)
+
+
 EDGE_CASES = [
     # B, V, Hh, W, H, D, S, dtype, coords range
     (1, 2, 1, 5, 3, 256, 3, torch.float32, (-0.2, 1.2)),     # widest head dim, fp32: 32 lanes x 2 vectors per row

@@ -61,3 +61,30 @@ def test_random_problem_matches_the_oracle(case, oracle):
         errs["dcoords"] = rel_err(dc, dc_ref)
     for name, e in errs.items():
         assert e < tol, (name, e, case)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_every_sample_at_the_same_place(dtype, oracle):
+    """All coordinates equal: one anchor per map row collects every sample of a tile, so its list
+    is longer than the work list's length buckets distinguish (576 entries) and all but two groups
+    of lanes of the gather pass have nothing to do.  Also the other extreme in the same map:
+    coordinates exactly on a pixel, where three of the four corner weights are zero."""
+    import ops
+    be = ops.backend
+    B, V, Hh, W, H, D, S = 1, 2, 2, 6, 6, 32, 16
+    L = W * H
+    g = torch.Generator().manual_seed(77)
+    q, k, v, dout = (torch.randn(B, V, Hh, L, D, generator=g).to(dtype) for _ in range(4))
+    dev = torch.device("cuda", 0)
+    for point in ((0.37, 0.61), (0.4, 0.8)):          # between pixels; exactly pixel (2, 4) of a 6x6 map
+        coords = torch.tensor(point).expand(B, V, L, V, S, 2).contiguous()
+        qd, kd, vd, dd, cd = (t.to(dev) for t in (q, k, v, dout, coords))
+        out, lse = be.forward_raw(qd, kd, vd, cd, W, H, 0.3)
+        dq, dk, dv, dc = be.backward_raw(qd, kd, vd, cd, out, lse, dd, W, H, 0.3, want_dcoords=True)
+        torch.cuda.synchronize()
+        o_ref, _ = oracle.forward(q, k, v, coords, W, H, 0.3)
+        dq_ref, dk_ref, dv_ref, dc_ref = oracle.backward(q, k, v, coords, dout, W, H, 0.3, with_dcoords=True)
+        tol = TOL[dtype]
+        for name, got, ref in (("out", out, o_ref), ("dq", dq, dq_ref), ("dk", dk, dk_ref), ("dv", dv, dv_ref),
+                               ("dcoords", dc, dc_ref)):
+            assert rel_err(got, ref) < tol, (name, point, rel_err(got, ref))
