@@ -667,6 +667,7 @@ def main():
         # (copy in, compute, copy out); every byte still crosses PCIe inside the timed region
         sizes = [int(x) for x in os.environ["BENCH_E2E_SIZES"].split(",")] if os.environ.get("BENCH_E2E_SIZES") else None
         pipe = be.HostPipeline(dev, cfg.W, cfg.H, cfg.sm_scale, sizes=sizes,
+                               compute_streams=int(os.environ.get("BENCH_E2E_STREAMS", "2")),
                                chunk=max(1, min(int(os.environ.get("BENCH_E2E_CHUNK", "8")), nb)))
 
         def estep(_record):

@@ -57,7 +57,7 @@ class HostPipeline:
     """
 
     def __init__(self, device, W: int, H: int, sm_scale: float, chunk: int = 8, flags: Optional[int] = None,
-                 direct_results: bool = False, sizes: Optional[Sequence[int]] = None):
+                 direct_results: bool = False, sizes: Optional[Sequence[int]] = None, compute_streams: int = 2):
         self.device = torch.device(device)
         self.W, self.H, self.sm_scale = int(W), int(H), float(sm_scale)
         self.chunk = max(1, int(chunk))
@@ -65,21 +65,24 @@ class HostPipeline:
         self.flags = flags
         self.direct_results = bool(direct_results)
         self.s_in = torch.cuda.Stream(self.device)
-        self.s_comp = torch.cuda.Stream(self.device)
+        # Chunks are independent, so consecutive chunks run on alternating compute streams: the last,
+        # partly filled wave of one chunk's kernels then shares the GPU with the first wave of the
+        # next chunk's instead of leaving SMs idle.
+        self.s_comps = [torch.cuda.Stream(self.device) for _ in range(max(1, int(compute_streams)))]
         self.s_out = torch.cuda.Stream(self.device)
         # With ``time_transfers = True`` every run brackets its copies in and its copies out with
         # timing events; ``transfer_rates()`` then gives the bandwidth they reached.
         self.time_transfers = False
         self._marks = None
 
-    def _to_device(self, hosts: Sequence[Optional[torch.Tensor]], b0: int, b1: int):
+    def _to_device(self, hosts: Sequence[Optional[torch.Tensor]], b0: int, b1: int, s_comp):
         out = []
         for t in hosts:
             if t is None:
                 out.append(None)
                 continue
             d = t[b0:b1].to(self.device, non_blocking=True)
-            d.record_stream(self.s_comp)
+            d.record_stream(s_comp)
             out.append(d)
         return out
 
@@ -101,7 +104,7 @@ class HostPipeline:
         cur = torch.cuda.current_stream(self.device)
         start = torch.cuda.Event()
         start.record(cur)
-        for s in (self.s_in, self.s_comp, self.s_out):
+        for s in (self.s_in, *self.s_comps, self.s_out):
             s.wait_event(start)
         marks = None
         if self.time_transfers:
@@ -117,31 +120,32 @@ class HostPipeline:
             schedule = list(zip(bounds[:-1], bounds[1:]))
         else:
             schedule = chunk_schedule(B, self.chunk)
-        for b0, b1 in schedule:
+        for step, (b0, b1) in enumerate(schedule):
+            s_comp = self.s_comps[step % len(self.s_comps)]
             with torch.cuda.stream(self.s_in):
-                d_q, d_k, d_v, d_c = self._to_device((q, k, v, coords), b0, b1)
+                d_q, d_k, d_v, d_c = self._to_device((q, k, v, coords), b0, b1, s_comp)
                 ready_fwd = torch.cuda.Event()
                 ready_fwd.record(self.s_in)
-                (d_do,) = self._to_device((dout,), b0, b1)
+                (d_do,) = self._to_device((dout,), b0, b1, s_comp)
                 ready_bwd = torch.cuda.Event()
                 ready_bwd.record(self.s_in)
             mirror = {n: results[n][b0:b1] for n in results if direct[n]}
             copies = []
-            self.s_comp.wait_event(ready_fwd)
-            with torch.cuda.stream(self.s_comp):
+            s_comp.wait_event(ready_fwd)
+            with torch.cuda.stream(s_comp):
                 o, lse = forward_raw(d_q, d_k, d_v, d_c, self.W, self.H, self.sm_scale, flags=self.flags,
                                      out_mirror=mirror.get("out"))
                 if not direct["out"]:
                     fwd_done = torch.cuda.Event()
-                    fwd_done.record(self.s_comp)
+                    fwd_done.record(s_comp)
                     copies.append((fwd_done, out, o))
                 if backward:
-                    self.s_comp.wait_event(ready_bwd)
+                    s_comp.wait_event(ready_bwd)
                     grads = backward_raw(d_q, d_k, d_v, d_c, o, lse, d_do, self.W, self.H, self.sm_scale,
                                          flags=self.flags,
                                          mirrors={n: t for n, t in mirror.items() if n != "out"} or None)
                     bwd_done = torch.cuda.Event()
-                    bwd_done.record(self.s_comp)
+                    bwd_done.record(s_comp)
                     copies += [(bwd_done, results[n], g) for n, g in zip(("dq", "dk", "dv"), grads) if not direct[n]]
             with torch.cuda.stream(self.s_out):
                 for event, host, dev_t in copies:
@@ -155,7 +159,7 @@ class HostPipeline:
             marks["in1"].record(self.s_in)
             marks["out1"].record(self.s_out)
             self._marks = marks
-        for s in (self.s_comp, self.s_out):
+        for s in (*self.s_comps, self.s_out):
             end = torch.cuda.Event()
             end.record(s)
             cur.wait_event(end)
