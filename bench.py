@@ -45,6 +45,8 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="C5")
     ap.add_argument("--mode", default="fwdbwd", choices=["fwdbwd", "fwd"])
+    ap.add_argument("--batch", type=int, default=0,
+                    help="override the configuration's batch size (e.g. 4: what one rank of an 8-GPU run of C5 holds)")
     ap.add_argument("--flags", type=lambda x: int(x, 0), default=0,
                     help="DSDPA_FLAG_* bits for every call (e.g. 0x10, rounded weights; 0x8, the scatter backward)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -432,6 +434,8 @@ def main():
         dist.init_process_group("nccl", device_id=dev, pg_options=opts)
 
     cfg = inp.config(args.config)
+    if args.batch > 0:
+        cfg = replace(cfg, B=args.batch)
     plan = part.shard_plan(cfg.B, cfg.Hh, world)
     shard = plan[rank]
     nb = shard.b1 - shard.b0
