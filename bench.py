@@ -662,17 +662,48 @@ def main():
     # ---- end to end: pinned host inputs in, results back out, through the operator's API
     e2e = None
     if not args.no_e2e:
-        hq, hk, hv, hdo, hc = (t.cpu().pin_memory() for t in (q, k, v, dout, coords))
+        # Several ranks: the GPUs of a box need not sit behind equally fast host links (measured
+        # here: four of eight at half the rate of the others while all transfer).  Every rank
+        # measures its link while the others measure theirs, and the batch is split for this leg
+        # in proportion to what each rank's pipeline can sustain (even when they are alike).
+        e_nb, links, shares = nb, None, None
+        eq, ek, ev_, edo, ec = q, k, v, dout, coords
+        if world > 1 and cfg.B >= world and os.environ.get("BENCH_E2E_BALANCE", "1") != "0":
+            barrier()
+            link = be.host.measure_link(dev)
+            links = [None] * world
+            dist.all_gather_object(links, link)
+            elem_in = in_bytes / nb
+            elem_out = (1 if fwd_only else 4) * q.numel() * q.element_size() / nb
+            weights = be.host.balance_weights(links, elem_in, elem_out, total_ms / args.steps * world / cfg.B)
+            if os.environ.get("BENCH_E2E_WEIGHTS"):      # a given split, to try the uneven path anywhere
+                weights = [float(x) for x in os.environ["BENCH_E2E_WEIGHTS"].split(",")]
+            e_plan = part.shard_plan(cfg.B, cfg.Hh, world, weights=weights)
+            shares = [s.b1 - s.b0 for s in e_plan]
+            if e_plan[rank] != shard:
+                parts = [draw(b) for b in range(e_plan[rank].b0, e_plan[rank].b1)]
+                eq, ek, ev_, edo = (torch.stack([p[i] for p in parts]).contiguous() for i in range(4))
+                ec = torch.stack([p[4] for p in parts]).contiguous()
+                del parts
+                e_nb = shares[rank]
+        hq, hk, hv, hdo, hc = (t.cpu().pin_memory() for t in (eq, ek, ev_, edo, ec))
+        del eq, ek, ev_, edo, ec
         h_out = [torch.empty_like(hq).pin_memory() for _ in range(1 if fwd_only else 4)]
         h2d = sum(t.numel() * t.element_size() for t in ((hq, hk, hv, hc) if fwd_only else (hq, hk, hv, hc, hdo)))
         d2h = sum(t.numel() * t.element_size() for t in h_out)
+        if world > 1:
+            moved = torch.tensor([h2d, d2h], dtype=torch.int64, device=dev)
+            dist.all_reduce(moved)
+            h2d_all, d2h_all = (int(x) for x in moved.tolist())
+        else:
+            h2d_all, d2h_all = h2d, d2h
 
         # the operator's front end for host tensors: chunks of batch elements on three streams
         # (copy in, compute, copy out); every byte still crosses PCIe inside the timed region
         sizes = [int(x) for x in os.environ["BENCH_E2E_SIZES"].split(",")] if os.environ.get("BENCH_E2E_SIZES") else None
         pipe = be.HostPipeline(dev, cfg.W, cfg.H, cfg.sm_scale, sizes=sizes,
                                compute_streams=int(os.environ.get("BENCH_E2E_STREAMS", "2")),
-                               chunk=max(1, min(int(os.environ.get("BENCH_E2E_CHUNK", "8")), nb)))
+                               chunk=max(1, min(int(os.environ.get("BENCH_E2E_CHUNK", "8")), e_nb)))
 
         def estep(_record):
             if fwd_only:
@@ -691,11 +722,14 @@ def main():
             dist.all_gather_object(per_rank, rates)
         else:
             per_rank = [rates]
-        # bytes are per rank; the job moves world times as much
+        # bytes of the whole job (summed over the ranks)
         e2e = {"value": cfg.query_heads / (e_ms * 1e-3), "unit": "query-heads/sec", "ms_per_step": e_ms,
-               "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
-               "chunks": pipe.sizes or [b1 - b0 for b0, b1 in be.host.chunk_schedule(nb, pipe.chunk)],
+               "h2d_bytes_per_step": h2d_all, "d2h_bytes_per_step": d2h_all,
+               "chunks": pipe.sizes or [b1 - b0 for b0, b1 in be.host.chunk_schedule(e_nb, pipe.chunk)],
                "transfers_per_rank": per_rank}
+        if shares is not None:
+            e2e["batch_elements_per_rank"] = shares
+            e2e["links_GBps_h2d_d2h"] = [[round(h, 1), round(d, 1)] for h, d in links]
         del hq, hk, hv, hdo, hc, h_out
 
     if rank != 0:

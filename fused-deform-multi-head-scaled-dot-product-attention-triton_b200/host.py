@@ -49,6 +49,49 @@ def chunk_schedule(B: int, chunk: int):
     return out
 
 
+def measure_link(device, nbytes: int = 64 << 20, reps: int = 4):
+    """Host link of one GPU under load: copies ``nbytes`` of pinned memory in and out at the same
+    time (two streams), ``reps`` times, and returns ``(h2d_GBps, d2h_GBps)``.  The ranks of a job
+    call it together (after a barrier), so that each sees what it gets while the others transfer
+    too; on some boxes the GPUs do not all sit behind equally fast links, and ``balance_weights``
+    turns the figures into a batch split."""
+    dev = torch.device(device)
+    h_in = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    h_out = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    d_in = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    d_out = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    torch.cuda.synchronize(dev)
+    for timed in (False, True):                      # one untimed round first
+        with torch.cuda.stream(s_in):
+            ev[0].record()
+            for _ in range(reps if timed else 1):
+                d_in.copy_(h_in, non_blocking=True)
+            ev[1].record()
+        with torch.cuda.stream(s_out):
+            ev[2].record()
+            for _ in range(reps if timed else 1):
+                h_out.copy_(d_out, non_blocking=True)
+            ev[3].record()
+        torch.cuda.synchronize(dev)
+    return (reps * nbytes / (ev[0].elapsed_time(ev[1]) * 1e6),
+            reps * nbytes / (ev[2].elapsed_time(ev[3]) * 1e6))
+
+
+def balance_weights(links, in_bytes: float, out_bytes: float, compute_ms: float, tolerance: float = 1.15):
+    """Batch-split weights for ``partition.shard_plan`` from every rank's ``measure_link`` result.
+
+    A rank's pipeline runs at the pace of its slowest stage, so a batch element costs it
+    ``max(compute_ms, in_bytes / h2d, out_bytes / d2h)`` (bytes per batch element, rates in GB/s)
+    and its weight is the inverse.  Ranks within ``tolerance`` of one another get equal weights:
+    an even split is not traded for measurement noise."""
+    cost = [max(float(compute_ms), in_bytes / (h * 1e6), out_bytes / (d * 1e6)) for h, d in links]
+    if max(cost) <= tolerance * min(cost):
+        return [1.0] * len(cost)
+    return [1.0 / c for c in cost]
+
+
 class HostPipeline:
     """Forward (+ backward) of the operator on host tensors, chunked over the batch.
 

@@ -45,10 +45,50 @@ def _split(n: int, parts: int) -> List[range]:
     return out
 
 
-def shard_plan(B: int, Hh: int, world: int) -> List[Shard]:
-    """One Shard per rank.  Batch-major; heads are split only when B < world."""
+def _split_weighted(n: int, weights: Sequence[float]) -> List[range]:
+    """Contiguous ranges of ``n`` items in proportion to ``weights`` (largest remainders first;
+    every part with a positive weight gets at least one item when there are enough)."""
+    w = [max(0.0, float(x)) for x in weights]
+    total = sum(w)
+    if total <= 0.0:
+        raise ValueError("weights must have a positive sum")
+    ideal = [n * x / total for x in w]
+    counts = [int(x) for x in ideal]
+    if n >= sum(1 for x in w if x > 0.0):
+        counts = [max(c, 1) if x > 0.0 else 0 for c, x in zip(counts, w)]
+    # hand out what is left (or take back what the minimum of one overspent) by remainder
+    order = sorted(range(len(w)), key=lambda i: ideal[i] - counts[i], reverse=True)
+    i = 0
+    while sum(counts) < n:
+        counts[order[i % len(order)]] += 1
+        i += 1
+    i = 0
+    while sum(counts) > n:
+        j = order[-1 - (i % len(order))]
+        if counts[j] > 1:
+            counts[j] -= 1
+        i += 1
+    out, lo = [], 0
+    for c in counts:
+        out.append(range(lo, lo + c))
+        lo += c
+    return out
+
+
+def shard_plan(B: int, Hh: int, world: int, weights: Optional[Sequence[float]] = None) -> List[Shard]:
+    """One Shard per rank.  Batch-major; heads are split only when B < world.
+
+    ``weights`` (one positive number per rank, e.g. each rank's measured throughput) splits the
+    batch in their proportion instead of evenly -- for boxes whose GPUs do not all sit behind
+    equally fast host links.  It needs B >= world."""
     if B <= 0 or Hh <= 0 or world <= 0:
         raise ValueError("B, Hh and world must be positive")
+    if weights is not None:
+        if len(weights) != world:
+            raise ValueError("one weight per rank")
+        if B < world:
+            raise ValueError("a weighted plan splits the batch only: it needs B >= world")
+        return [Shard(r.start, r.stop, 0, Hh) for r in _split_weighted(B, weights)]
     if B >= world:
         return [Shard(r.start, r.stop, 0, Hh) for r in _split(B, world)]
     # fewer batch elements than ranks: give each batch element a group of ranks that

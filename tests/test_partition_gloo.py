@@ -42,13 +42,46 @@ def test_plan_splits_heads_only_when_batches_run_out():
     assert sum(1 for s in plan if s.empty) == 2
 
 
+def test_weighted_plan_splits_the_batch_in_proportion():
+    sizes = lambda plan: [s.b1 - s.b0 for s in plan]
+    assert sizes(part.shard_plan(32, 16, 8, weights=[1.0] * 8)) == [4] * 8
+    # four ranks behind links of half the rate: 1/6.2 against 1/3.8 per batch element
+    plan = part.shard_plan(32, 16, 8, weights=[1 / 6.2] * 4 + [1 / 3.8] * 4)
+    assert sizes(plan) == [3, 3, 3, 3, 5, 5, 5, 5]
+    assert [s.b0 for s in plan] == [0, 3, 6, 9, 12, 17, 22, 27] and plan[-1].b1 == 32
+    assert all(s.h0 == 0 and s.h1 == 16 for s in plan)
+    # nobody with a positive weight is left without work while there is enough of it
+    assert sizes(part.shard_plan(8, 4, 8, weights=[1, 1, 1, 1, 9, 9, 9, 9])) == [1] * 8
+    assert sum(sizes(part.shard_plan(9, 4, 8, weights=[1, 1, 1, 1, 9, 9, 9, 9]))) == 9
+    assert sizes(part.shard_plan(32, 4, 2, weights=[1, 3])) == [8, 24]
+    with pytest.raises(ValueError):
+        part.shard_plan(2, 16, 8, weights=[1.0] * 8)       # a weighted plan never splits heads
+    with pytest.raises(ValueError):
+        part.shard_plan(8, 16, 2, weights=[1.0] * 3)
+    with pytest.raises(ValueError):
+        part.shard_plan(8, 16, 2, weights=[0.0, 0.0])
+
+
+def test_balance_weights_follow_the_slowest_stage():
+    host = ops.backend.host
+    # (h2d, d2h) GB/s per rank; 64 MB in and 51 MB out per batch element, 3.75 ms of kernels
+    links = [(11.7, 8.2)] * 4 + [(21.3, 13.5)] * 4
+    w = host.balance_weights(links, 64.2e6, 51.4e6, 3.75)
+    assert w[0] == pytest.approx(1 / (51.4 / 8.2), rel=1e-6)        # copy-out bound
+    assert w[4] == pytest.approx(1 / (51.4 / 13.5), rel=1e-6)
+    assert [s.b1 - s.b0 for s in part.shard_plan(32, 16, 8, weights=w)] == [3, 3, 3, 3, 5, 5, 5, 5]
+    # alike within the tolerance: an even split; fast links: the kernels set the pace for everybody
+    assert host.balance_weights([(20.0, 13.0), (21.0, 13.5)], 64.2e6, 51.4e6, 3.75) == [1.0, 1.0]
+    assert host.balance_weights([(50.0, 50.0), (25.0, 25.0)], 64.2e6, 51.4e6, 3.75) == [1.0, 1.0]
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, B, Hh, result_path):
+def _worker(rank, world, port, B, Hh, result_path, weights=None):
     sys.path.insert(0, str(ROOT))
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -58,7 +91,7 @@ def _worker(rank, world, port, B, Hh, result_path):
     inp, prt = _ops.backend.inputs, _ops.backend.partition
     cfg = replace(inp.CONFIGS["C2"], B=B, Hh=Hh, V=2, S=4, W=6, H=5)
     q, k, v, coords, _ = inp.make_inputs(cfg)
-    plan = prt.shard_plan(cfg.B, cfg.Hh, world)
+    plan = prt.shard_plan(cfg.B, cfg.Hh, world, weights=weights)
 
     def fn(qs, ks, vs, cs):
         return orc.forward(qs, ks, vs, cs, cfg.W, cfg.H, cfg.sm_scale, nthreads=1)[0]
@@ -86,6 +119,15 @@ def test_two_rank_sharded_run_matches_unsharded(tmp_path, B, Hh):
     out = torch.load(result)
     assert out["equal"], "gathered sharded output differs from the unsharded one"
     assert out["shape"][0] == B and out["shape"][2] == Hh
+
+
+def test_two_rank_run_with_a_weighted_plan_matches_unsharded(tmp_path):
+    from oracle import oracle as orc
+    orc.build()
+    result = tmp_path / "result.pt"
+    mp.spawn(_worker, args=(2, _free_port(), 4, 2, str(result), [1.0, 3.0]), nprocs=2, join=True)
+    out = torch.load(result)
+    assert out["equal"], "gathered output of the 1 + 3 split differs from the unsharded one"
 
 
 def _failing_worker(rank, world, port, result_dir):
