@@ -774,7 +774,7 @@ def main():
         # dram__bytes_read.sum + dram__bytes_write.sum of the forward kernel, NOT measured in this run:
         # from the committed ncu capture of a B=2 case of this configuration, scaled to this launch
         # by its query-heads (the traffic grows in proportion to the batch)
-        "traffic": (119.0e6 / 200704) * qh_rank if cfg.name == "C5" else None,
+        "traffic": (119.2e6 / 200704) * qh_rank if cfg.name == "C5" else None,
         "traffic_source": "profiles/c5_b2_kernels_full_set.md (ncu, B=2 case, scaled by query-heads)" if cfg.name == "C5" else None,
         "l2_read_peak": l2_peak,
         "shared_patterns_GBps": {str(k_): v_ for k_, v_ in peaks["shared"].items()},

@@ -176,12 +176,12 @@ GatherPlan plan_gather(const dsdpa_problem& p) {
     // entries hold byte offsets into the tile's rows and scalars as 32-bit fields; one segment's
     // entry count must stay an int
     while (qb_max > 2 && qb_max * p.S * 2 > (1ll << 30)) qb_max -= 2;
-    // The index builder keeps one histogram over the anchors per sample-taking warp: eight when
-    // they fit, fewer for large maps (slower to build, same lists).
-    // (beside the histograms: the lists' first entries [A], 256 partial sums, the length buckets)
-    const long long fixed_ints = 256 + (long long)kMaxSlabs * kLenBuckets;
+    // The index builder keeps one histogram over the anchors per sample-taking warp: one per warp
+    // when they fit, fewer for large maps (slower to build, same lists).
+    // (beside the histograms: the lists' first entries [A], a partial sum per thread, the length buckets)
+    const long long fixed_ints = kIndexWarpsDefault * 32 + (long long)kMaxSlabs * kLenBuckets;
     long long nhist = ((long long)kPlanSmemMax / 4 - 16 - fixed_ints) / A - 1;
-    if (nhist > 8) nhist = 8;
+    if (nhist > kIndexWarpsDefault) nhist = kIndexWarpsDefault;
     if (qb_max < 2 || nhist < 1 || A + 1 >= (1ll << 30)) return g;  // ok = false
     size_t index_smem = (size_t)((nhist + 1) * A + fixed_ints) * sizeof(int);
     {

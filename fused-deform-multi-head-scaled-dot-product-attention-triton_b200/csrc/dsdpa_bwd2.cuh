@@ -57,7 +57,7 @@ struct IndexParams {
 constexpr int kMaxSlabs = 4;
 constexpr int kLenBuckets = 512;   // list lengths are sorted exactly up to this, longer ones count as equal
 
-constexpr int kIndexWarpsDefault = 8;
+constexpr int kIndexWarpsDefault = 16;   // the build is bound by latency: as many warps as the histograms allow
 
 // One sample's footprint for the index: anchor column, the two map rows and the 1-D weights
 // (zero where the column / row lies outside the map), from the same arithmetic as
@@ -90,7 +90,7 @@ __device__ __forceinline__ void decode_footprint(float cx, float cy, int W, int 
 // ints.  (A template so that the header can be included by several translation units.)
 template <int NWARPS>
 __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexParams p) {
-    static_assert(NWARPS == 8, "the scan below handles 256 partial sums");
+    static_assert(NWARPS >= 1 && NWARPS <= 32, "one warp scans the NWARPS*32 partial sums, NWARPS per lane");
     extern __shared__ __align__(16) unsigned char smem[];
     int* cnt = reinterpret_cast<int*>(smem);
     int* lens = cnt + p.nhist * p.A;       // first entry of every anchor's list, later its length
@@ -131,18 +131,29 @@ __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexPar
         return f.y[r] * AW + f.a;
     };
 
+    // Both passes over the samples fetch the coordinates of kAhead steps (32 samples each) before
+    // they work on the first: the loop is bound by the latency of those loads, not by their volume.
+    constexpr int kAhead = 4;
+
     // pass 1: per-warp histogram of anchors
-    for (int base = wbeg; base < wend; base += 32) {
-        const int smp = base + lane;
-        if (smp < wend) {
-            const float2 c = coord_of(smp);
-            Footprint f;
-            decode_footprint(c.x, c.y, p.W, p.H, p.hw, p.hh, f);
+    for (int base = wbeg; base < wend; base += 32 * kAhead) {
+        float2 c[kAhead];
 #pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                float wl, wr;
-                const int a = entry_of(f, r, wl, wr);
-                if (a >= 0 && in_range(a, p.A, p.err)) atomicAdd(&mycnt[a], 1);
+        for (int u = 0; u < kAhead; ++u) {
+            const int smp = base + u * 32 + lane;
+            c[u] = smp < wend ? coord_of(smp) : make_float2(0.0f, 0.0f);
+        }
+#pragma unroll
+        for (int u = 0; u < kAhead; ++u) {
+            if (base + u * 32 + lane < wend) {
+                Footprint f;
+                decode_footprint(c[u].x, c[u].y, p.W, p.H, p.hw, p.hh, f);
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    float wl, wr;
+                    const int a = entry_of(f, r, wl, wr);
+                    if (a >= 0 && in_range(a, p.A, p.err)) atomicAdd(&mycnt[a], 1);
+                }
             }
         }
     }
@@ -159,10 +170,10 @@ __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexPar
     part[threadIdx.x] = local;
     __syncthreads();
     if (warp == 0) {
-        // scan of 256 partial sums by one warp, 8 per lane
-        int v[8], sum = 0;
+        // scan of the NWARPS*32 partial sums by one warp, NWARPS per lane
+        int v[NWARPS], sum = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { v[i] = part[lane * 8 + i]; sum += v[i]; }
+        for (int i = 0; i < NWARPS; ++i) { v[i] = part[lane * NWARPS + i]; sum += v[i]; }
         int incl = sum;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -171,7 +182,7 @@ __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexPar
         }
         int run = incl - sum;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { part[lane * 8 + i] = run; run += v[i]; }
+        for (int i = 0; i < NWARPS; ++i) { part[lane * NWARPS + i] = run; run += v[i]; }
     }
     __syncthreads();
     int run = part[threadIdx.x];
@@ -189,40 +200,50 @@ __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexPar
     // pass 3: scatter in canonical order (32 samples at a time, map row 0 before map row 1),
     // ranks of equal anchors inside the warp from match_any
     uint4* entries = p.entries + (size_t)seg * (size_t)p.seg_entries;
-    for (int base = wbeg; base < wend; base += 32) {
-        const int smp = base + lane;
-        Footprint f;
-        f.a = 0; f.y[0] = f.y[1] = 0;
-        f.wx[0] = f.wx[1] = f.wy[0] = f.wy[1] = 0.0f;
-        uint32_t roff = 0, soff = 0;
-        if (smp < wend) {
-            const float2 c = coord_of(smp);
-            decode_footprint(c.x, c.y, p.W, p.H, p.hw, p.hh, f);
-            // what the gather pass needs of the sample: where its query's row starts in the
-            // tile and where its pair of scalars lies among the tile's, both in bytes
-            roff = (uint32_t)(smp / p.S) * (uint32_t)p.rowb;
-            soff = (uint32_t)smp * 8u;
+    for (int base4 = wbeg; base4 < wend; base4 += 32 * kAhead) {
+        float2 c[kAhead];
+#pragma unroll
+        for (int u = 0; u < kAhead; ++u) {
+            const int smp = base4 + u * 32 + lane;
+            c[u] = smp < wend ? coord_of(smp) : make_float2(0.0f, 0.0f);
         }
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            float wl, wr;
-            const int a = entry_of(f, r, wl, wr);
-            const bool valid = a >= 0 && in_range(a, p.A, p.err);
-            const unsigned vmask = __ballot_sync(0xffffffffu, valid);
-            if (valid) {
-                const unsigned same = __match_any_sync(vmask, a);
-                const int leader = __ffs(same) - 1;
-                const int rank = __popc(same & ((1u << lane) - 1u));
-                int start = 0;
-                if (lane == leader) {
-                    start = mycnt[a];
-                    mycnt[a] = start + __popc(same);
-                }
-                start = __shfl_sync(same, start, leader);
-                if (in_range(start + rank, p.seg_entries, p.err))
-                    entries[start + rank] = make_uint4(roff, soff, __float_as_uint(wl), __float_as_uint(wr));
+        for (int u = 0; u < kAhead; ++u) {
+            const int base = base4 + u * 32;
+            if (base >= wend) break;            // the same for the whole warp
+            const int smp = base + lane;
+            Footprint f;
+            f.a = 0; f.y[0] = f.y[1] = 0;
+            f.wx[0] = f.wx[1] = f.wy[0] = f.wy[1] = 0.0f;
+            uint32_t roff = 0, soff = 0;
+            if (smp < wend) {
+                decode_footprint(c[u].x, c[u].y, p.W, p.H, p.hw, p.hh, f);
+                // what the gather pass needs of the sample: where its query's row starts in the
+                // tile and where its pair of scalars lies among the tile's, both in bytes
+                roff = (uint32_t)(smp / p.S) * (uint32_t)p.rowb;
+                soff = (uint32_t)smp * 8u;
             }
-            __syncwarp();
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                float wl, wr;
+                const int a = entry_of(f, r, wl, wr);
+                const bool valid = a >= 0 && in_range(a, p.A, p.err);
+                const unsigned vmask = __ballot_sync(0xffffffffu, valid);
+                if (valid) {
+                    const unsigned same = __match_any_sync(vmask, a);
+                    const int leader = __ffs(same) - 1;
+                    const int rank = __popc(same & ((1u << lane) - 1u));
+                    int start = 0;
+                    if (lane == leader) {
+                        start = mycnt[a];
+                        mycnt[a] = start + __popc(same);
+                    }
+                    start = __shfl_sync(same, start, leader);
+                    if (in_range(start + rank, p.seg_entries, p.err))
+                        entries[start + rank] = make_uint4(roff, soff, __float_as_uint(wl), __float_as_uint(wr));
+                }
+                __syncwarp();
+            }
         }
     }
     __syncthreads();
@@ -250,9 +271,9 @@ __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexPar
         part[threadIdx.x] = sum;
         __syncthreads();
         if (warp == 0) {
-            int v[8], tot = 0;
+            int v[NWARPS], tot = 0;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) { v[i] = part[lane * 8 + i]; tot += v[i]; }
+            for (int i = 0; i < NWARPS; ++i) { v[i] = part[lane * NWARPS + i]; tot += v[i]; }
             int incl = tot;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -261,7 +282,7 @@ __global__ void __launch_bounds__(NWARPS * 32) index_build_kernel(const IndexPar
             }
             int r2 = incl - tot;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) { part[lane * 8 + i] = r2; r2 += v[i]; }
+            for (int i = 0; i < NWARPS; ++i) { part[lane * NWARPS + i] = r2; r2 += v[i]; }
         }
         __syncthreads();
         int at = part[threadIdx.x];
