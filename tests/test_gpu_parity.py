@@ -225,6 +225,18 @@ def test_host_pipeline_with_given_chunk_sizes(backend):
                                                                                dk=dk, dv=dv)
 
 
+def test_link_probe_feeds_a_weighted_plan(backend):
+    """The host-link probe returns two positive rates, and a plan weighted by them covers the
+    batch with contiguous shards (one GPU: one rank's figures stand in for several)."""
+    h2d, d2h = backend.host.measure_link(torch.device("cuda", 0), nbytes=8 << 20, reps=2)
+    assert h2d > 0.1 and d2h > 0.1
+    weights = backend.host.balance_weights([(h2d, d2h), (h2d / 2, d2h / 2), (h2d, d2h)], 64.2e6, 51.4e6, 0.01)
+    plan = backend.partition.shard_plan(12, 4, 3, weights=weights)
+    sizes = [s.b1 - s.b0 for s in plan]
+    assert sum(sizes) == 12 and sizes[1] < sizes[0] == sizes[2]
+    assert [s.b0 for s in plan] == [0, sizes[0], sizes[0] + sizes[1]]
+
+
 EDGE_CASES = [
     # B, V, Hh, W, H, D, S, dtype, coords range
     (1, 2, 1, 5, 3, 256, 3, torch.float32, (-0.2, 1.2)),     # widest head dim, fp32: 32 lanes x 2 vectors per row
