@@ -662,54 +662,78 @@ def main():
     # ---- end to end: pinned host inputs in, results back out, through the operator's API
     e2e = None
     if not args.no_e2e:
+        sizes = [int(x) for x in os.environ["BENCH_E2E_SIZES"].split(",")] if os.environ.get("BENCH_E2E_SIZES") else None
+
+        class Leg:
+            """Pinned host tensors of a batch range and the operator's front end for them: chunks
+            of batch elements on copy-in, compute and copy-out streams; every byte crosses PCIe
+            inside the timed region."""
+
+            def __init__(self, tensors, n_elements, head_parts):
+                self.nb = n_elements
+                self.hq, self.hk, self.hv, self.hdo, self.hc = (t.cpu().pin_memory() for t in tensors)
+                self.h_out = [torch.empty_like(self.hq).pin_memory() for _ in range(1 if fwd_only else 4)]
+                ins = (self.hq, self.hk, self.hv, self.hc) if fwd_only else (self.hq, self.hk, self.hv, self.hc, self.hdo)
+                self.h2d = sum(t.numel() * t.element_size() for t in ins)
+                self.d2h = sum(t.numel() * t.element_size() for t in self.h_out)
+                self.pipe = be.HostPipeline(dev, cfg.W, cfg.H, cfg.sm_scale, sizes=sizes,
+                                            compute_streams=int(os.environ.get("BENCH_E2E_STREAMS", "2")),
+                                            head_parts=head_parts,
+                                            chunk=max(1, min(int(os.environ.get("BENCH_E2E_CHUNK", "8")), n_elements)))
+
+            def step(self, _record):
+                o = self.h_out
+                if fwd_only:
+                    self.pipe.run(self.hq, self.hk, self.hv, self.hc, out=o[0])
+                else:
+                    self.pipe.run(self.hq, self.hk, self.hv, self.hc, self.hdo, out=o[0], dq=o[1], dk=o[2], dv=o[3])
+
+        head_parts = int(os.environ.get("BENCH_E2E_HEAD_PARTS", "1"))
+        leg = Leg((q, k, v, dout, coords), nb, head_parts)
         # Several ranks: the GPUs of a box need not sit behind equally fast host links (measured
-        # here: four of eight at half the rate of the others while all transfer).  Every rank
-        # measures its link while the others measure theirs, and the batch is split for this leg
-        # in proportion to what each rank's pipeline can sustain (even when they are alike).
-        e_nb, links, shares = nb, None, None
-        eq, ek, ev_, edo, ec = q, k, v, dout, coords
+        # here: with all eight ranks transferring, four get half the rate of the other four).  The
+        # leg calibrates itself: every rank times its pipeline over its even share, the times per
+        # batch element become weights, and the batch is split again in their proportion (like
+        # ranks share a weight, so a box of equal links keeps the even split).  A rank whose copies
+        # take longer than its kernels also cuts its first and last element into head groups.
+        shares, costs = None, None
         if world > 1 and cfg.B >= world and os.environ.get("BENCH_E2E_BALANCE", "1") != "0":
+            for _ in range(2):
+                leg.step(False)
+            torch.cuda.synchronize()
             barrier()
-            link = be.host.measure_link(dev)
-            links = [None] * world
-            dist.all_gather_object(links, link)
-            elem_in = in_bytes / nb
-            elem_out = (1 if fwd_only else 4) * q.numel() * q.element_size() / nb
-            weights = be.host.balance_weights(links, elem_in, elem_out, total_ms / args.steps * world / cfg.B)
+            a, b = ev(), ev()
+            a.record()
+            for _ in range(2):
+                leg.step(False)
+            b.record()
+            torch.cuda.synchronize()
+            mine = a.elapsed_time(b) / 2 / nb
+            costs = [None] * world
+            dist.all_gather_object(costs, mine)
+            weights = be.host.weights_from_costs(costs)
             if os.environ.get("BENCH_E2E_WEIGHTS"):      # a given split, to try the uneven path anywhere
                 weights = [float(x) for x in os.environ["BENCH_E2E_WEIGHTS"].split(",")]
+            kernels_ms = total_ms / args.steps * world / cfg.B
+            if "BENCH_E2E_HEAD_PARTS" not in os.environ and mine > 1.3 * kernels_ms and cfg.Hh >= 4:
+                head_parts = 4
             e_plan = part.shard_plan(cfg.B, cfg.Hh, world, weights=weights)
             shares = [s.b1 - s.b0 for s in e_plan]
-            if e_plan[rank] != shard:
+            if e_plan[rank] != shard or head_parts != leg.pipe.head_parts:
+                del leg
                 parts = [draw(b) for b in range(e_plan[rank].b0, e_plan[rank].b1)]
-                eq, ek, ev_, edo = (torch.stack([p[i] for p in parts]).contiguous() for i in range(4))
-                ec = torch.stack([p[4] for p in parts]).contiguous()
+                tensors = [torch.stack([p[i] for p in parts]).contiguous() for i in (0, 1, 2, 3, 4)]
                 del parts
-                e_nb = shares[rank]
-        hq, hk, hv, hdo, hc = (t.cpu().pin_memory() for t in (eq, ek, ev_, edo, ec))
-        del eq, ek, ev_, edo, ec
-        h_out = [torch.empty_like(hq).pin_memory() for _ in range(1 if fwd_only else 4)]
-        h2d = sum(t.numel() * t.element_size() for t in ((hq, hk, hv, hc) if fwd_only else (hq, hk, hv, hc, hdo)))
-        d2h = sum(t.numel() * t.element_size() for t in h_out)
+                leg = Leg(tensors, shares[rank], head_parts)
+                del tensors
         if world > 1:
-            moved = torch.tensor([h2d, d2h], dtype=torch.int64, device=dev)
+            moved = torch.tensor([leg.h2d, leg.d2h], dtype=torch.int64, device=dev)
             dist.all_reduce(moved)
             h2d_all, d2h_all = (int(x) for x in moved.tolist())
         else:
-            h2d_all, d2h_all = h2d, d2h
+            h2d_all, d2h_all = leg.h2d, leg.d2h
+        pipe, estep, e_nb = leg.pipe, leg.step, leg.nb
 
-        # the operator's front end for host tensors: chunks of batch elements on three streams
-        # (copy in, compute, copy out); every byte still crosses PCIe inside the timed region
-        sizes = [int(x) for x in os.environ["BENCH_E2E_SIZES"].split(",")] if os.environ.get("BENCH_E2E_SIZES") else None
-        pipe = be.HostPipeline(dev, cfg.W, cfg.H, cfg.sm_scale, sizes=sizes,
-                               compute_streams=int(os.environ.get("BENCH_E2E_STREAMS", "2")),
-                               chunk=max(1, min(int(os.environ.get("BENCH_E2E_CHUNK", "8")), e_nb)))
-
-        def estep(_record):
-            if fwd_only:
-                pipe.run(hq, hk, hv, hc, out=h_out[0])
-            else:
-                pipe.run(hq, hk, hv, hc, hdo, out=h_out[0], dq=h_out[1], dk=h_out[2], dv=h_out[3])
         e_total = timed(estep, max(2, min(args.steps, 5)), 3)
         e_ms = e_total / max(2, min(args.steps, 5))
         # what the copies of one more step (outside the timed region) sustained on every rank
@@ -725,12 +749,13 @@ def main():
         # bytes of the whole job (summed over the ranks)
         e2e = {"value": cfg.query_heads / (e_ms * 1e-3), "unit": "query-heads/sec", "ms_per_step": e_ms,
                "h2d_bytes_per_step": h2d_all, "d2h_bytes_per_step": d2h_all,
-               "chunks": pipe.sizes or [b1 - b0 for b0, b1 in be.host.chunk_schedule(e_nb, pipe.chunk)],
+               "chunks": [b1 - b0 if (h0, h1) == (0, cfg.Hh) else f"{h1 - h0}/{cfg.Hh} heads"
+                          for b0, b1, h0, h1 in pipe._schedule(e_nb, cfg.Hh)],
                "transfers_per_rank": per_rank}
         if shares is not None:
             e2e["batch_elements_per_rank"] = shares
-            e2e["links_GBps_h2d_d2h"] = [[round(h, 1), round(d, 1)] for h, d in links]
-        del hq, hk, hv, hdo, hc, h_out
+            e2e["calibration_ms_per_batch_element"] = [round(c, 2) for c in costs]
+        del leg, pipe, estep
 
     if rank != 0:
         if world > 1:

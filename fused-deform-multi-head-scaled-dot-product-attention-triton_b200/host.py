@@ -49,47 +49,86 @@ def chunk_schedule(B: int, chunk: int):
     return out
 
 
-def measure_link(device, nbytes: int = 64 << 20, reps: int = 4):
+def measure_link(device, nbytes: int = 64 << 20, reps: int = 8):
     """Host link of one GPU under load: copies ``nbytes`` of pinned memory in and out at the same
-    time (two streams), ``reps`` times, and returns ``(h2d_GBps, d2h_GBps)``.  The ranks of a job
-    call it together (after a barrier), so that each sees what it gets while the others transfer
-    too; on some boxes the GPUs do not all sit behind equally fast links, and ``balance_weights``
-    turns the figures into a batch split."""
+    time (two streams), ``reps`` times, and returns ``(h2d_GBps, d2h_GBps)``, each the median over
+    the repetitions.  The ranks of a job call it together (after a barrier), so that each sees
+    what it gets while the others transfer too; on some boxes the GPUs do not all sit behind
+    equally fast links, and ``balance_weights`` turns the figures into a batch split."""
     dev = torch.device(device)
     h_in = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
     h_out = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
     d_in = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     d_out = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
     s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
     torch.cuda.synchronize(dev)
-    for timed in (False, True):                      # one untimed round first
-        with torch.cuda.stream(s_in):
-            ev[0].record()
-            for _ in range(reps if timed else 1):
-                d_in.copy_(h_in, non_blocking=True)
-            ev[1].record()
-        with torch.cuda.stream(s_out):
-            ev[2].record()
-            for _ in range(reps if timed else 1):
-                h_out.copy_(d_out, non_blocking=True)
-            ev[3].record()
-        torch.cuda.synchronize(dev)
-    return (reps * nbytes / (ev[0].elapsed_time(ev[1]) * 1e6),
-            reps * nbytes / (ev[2].elapsed_time(ev[3]) * 1e6))
+    marks_in = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 2)]
+    marks_out = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 2)]
+    with torch.cuda.stream(s_in):
+        for i in range(reps + 1):                    # the first repetition is not counted
+            marks_in[i].record()
+            d_in.copy_(h_in, non_blocking=True)
+        marks_in[reps + 1].record()
+    with torch.cuda.stream(s_out):
+        for i in range(reps + 1):
+            marks_out[i].record()
+            h_out.copy_(d_out, non_blocking=True)
+        marks_out[reps + 1].record()
+    torch.cuda.synchronize(dev)
+
+    def median_rate(marks):
+        ms = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(1, reps + 1))
+        mid = ms[len(ms) // 2] if len(ms) % 2 else 0.5 * (ms[len(ms) // 2 - 1] + ms[len(ms) // 2])
+        return nbytes / (mid * 1e6)
+    return median_rate(marks_in), median_rate(marks_out)
 
 
-def balance_weights(links, in_bytes: float, out_bytes: float, compute_ms: float, tolerance: float = 1.15):
-    """Batch-split weights for ``partition.shard_plan`` from every rank's ``measure_link`` result.
+def _element_costs(links, in_bytes: float, out_bytes: float, compute_ms: float):
+    return [max(float(compute_ms), in_bytes / (h * 1e6), out_bytes / (d * 1e6)) for h, d in links]
 
-    A rank's pipeline runs at the pace of its slowest stage, so a batch element costs it
-    ``max(compute_ms, in_bytes / h2d, out_bytes / d2h)`` (bytes per batch element, rates in GB/s)
-    and its weight is the inverse.  Ranks within ``tolerance`` of one another get equal weights:
-    an even split is not traded for measurement noise."""
-    cost = [max(float(compute_ms), in_bytes / (h * 1e6), out_bytes / (d * 1e6)) for h, d in links]
-    if max(cost) <= tolerance * min(cost):
-        return [1.0] * len(cost)
-    return [1.0 / c for c in cost]
+
+def weights_from_costs(costs: Sequence[float], tolerance: float = 1.25):
+    """Batch-split weights for ``partition.shard_plan`` from what one batch element costs every
+    rank (any unit; e.g. the time of a calibration run of its ``HostPipeline`` over its share,
+    divided by the share).  The weight is the inverse cost.  Ranks whose costs lie within
+    ``tolerance`` of one another form a group and share the group's mean cost: an even split is
+    not traded for measurement noise, neither over the whole job nor inside a group."""
+    cost = [float(c) for c in costs]
+    if not cost or min(cost) <= 0.0:
+        raise ValueError("costs must be positive")
+    order = sorted(range(len(cost)), key=lambda r: cost[r])
+    shared = [0.0] * len(cost)
+    i = 0
+    while i < len(order):
+        j = i
+        while j + 1 < len(order) and cost[order[j + 1]] <= tolerance * cost[order[i]]:
+            j += 1
+        group = order[i:j + 1]
+        mean = sum(cost[r] for r in group) / len(group)
+        for r in group:
+            shared[r] = mean
+        i = j + 1
+    return [1.0 / c for c in shared]
+
+
+def balance_weights(links, in_bytes: float, out_bytes: float, compute_ms: float, tolerance: float = 1.25):
+    """The same from every rank's ``measure_link`` result, without running the operator: a rank's
+    pipeline runs at the pace of its slowest stage, so a batch element costs it
+    ``max(compute_ms, in_bytes / h2d, out_bytes / d2h)`` (bytes per batch element, rates in GB/s).
+    A probe of bare copies does not see how the copies of a real run interleave with the kernels;
+    where the job can afford a calibration step, ``weights_from_costs`` of measured step times is
+    the better input."""
+    return weights_from_costs(_element_costs(links, in_bytes, out_bytes, compute_ms), tolerance)
+
+
+def suggest_head_parts(link, in_bytes: float, out_bytes: float, compute_ms: float, heads: int, parts: int = 4) -> int:
+    """``head_parts`` for a ``HostPipeline`` behind ``link`` (a ``measure_link`` result): cutting
+    the first and last batch element into head groups pays when the copies of a batch element
+    take longer than its kernels (measured: 8 ranks on a box with shared links, -3%), and costs
+    a little when they do not (one rank on a fast link, +0.3%)."""
+    if heads < parts:
+        return 1
+    return parts if _element_costs([link], in_bytes, out_bytes, compute_ms)[0] > float(compute_ms) else 1
 
 
 class HostPipeline:
@@ -102,11 +141,19 @@ class HostPipeline:
     host memory over PCIe while they run.  That leaves nothing to copy out at the end, but the
     stores hold the kernels back (C5 on a B200: +4% kernel time), more than the short last copy
     of the tapered schedule costs, so it is not the default.
+
+    ``head_parts`` > 1 cuts the first and the last batch element further, into that many groups of
+    heads ((batch, head) slices are independent too): the kernels start after a copy of a fraction
+    of an element and only as much is left to copy out when they end.  It pays where the host link
+    is slow against the kernels (several ranks sharing a box's links); a head group of one element
+    is V separate blocks of every tensor, so it costs V small copies per tensor and direction.
     """
 
     def __init__(self, device, W: int, H: int, sm_scale: float, chunk: int = 8, flags: Optional[int] = None,
-                 direct_results: bool = False, sizes: Optional[Sequence[int]] = None, compute_streams: int = 2):
+                 direct_results: bool = False, sizes: Optional[Sequence[int]] = None, compute_streams: int = 2,
+                 head_parts: int = 1):
         self.device = torch.device(device)
+        self.head_parts = max(1, int(head_parts))
         self.W, self.H, self.sm_scale = int(W), int(H), float(sm_scale)
         self.chunk = max(1, int(chunk))
         self.sizes = list(sizes) if sizes else None   # explicit chunk sizes (must add up to the batch)
@@ -133,6 +180,42 @@ class HostPipeline:
             d.record_stream(s_comp)
             out.append(d)
         return out
+
+    def _heads_to_device(self, hosts: Sequence[Optional[torch.Tensor]], b: int, h0: int, h1: int, s_comp):
+        """Heads h0..h1 of batch element b as compact device tensors [1, V, h1-h0, L, D]: one copy
+        per view (each view's run of heads is contiguous on both sides)."""
+        out = []
+        for t in hosts:
+            if t is None:
+                out.append(None)
+                continue
+            d = torch.empty((1, t.shape[1], h1 - h0) + tuple(t.shape[3:]), dtype=t.dtype, device=self.device)
+            for view in range(t.shape[1]):
+                d[0, view].copy_(t[b, view, h0:h1], non_blocking=True)
+            d.record_stream(s_comp)
+            out.append(d)
+        return out
+
+    def _schedule(self, B: int, Hh: int):
+        """Chunks as (b0, b1, h0, h1)."""
+        if self.sizes is not None:
+            if sum(self.sizes) != B or min(self.sizes) < 1:
+                raise ValueError(f"chunk sizes {self.sizes} do not cover a batch of {B}")
+            bounds = [sum(self.sizes[:i]) for i in range(len(self.sizes) + 1)]
+            batches = list(zip(bounds[:-1], bounds[1:]))
+        else:
+            batches = chunk_schedule(B, self.chunk)
+        parts = min(self.head_parts, Hh)
+        if self.direct_results:
+            parts = 1       # a head group is not a contiguous block of the result: no direct stores
+        chunks = []
+        for i, (b0, b1) in enumerate(batches):
+            if parts > 1 and b1 - b0 == 1 and i in (0, len(batches) - 1):
+                cuts = [Hh * j // parts for j in range(parts + 1)]
+                chunks += [(b0, b1, h0, h1) for h0, h1 in zip(cuts[:-1], cuts[1:]) if h1 > h0]
+            else:
+                chunks.append((b0, b1, 0, Hh))
+        return chunks
 
     def run(self, q, k, v, coords, dout=None, *, out, dq=None, dk=None, dv=None):
         """All arguments are host tensors (pinned for the copies to be asynchronous) with the
@@ -161,29 +244,35 @@ class HostPipeline:
             marks["bytes_in"] = sum(t.numel() * t.element_size() for t in (q, k, v, coords, dout) if t is not None)
             marks["bytes_out"] = sum(t.numel() * t.element_size() for n, t in results.items() if not direct[n])
             first_out = True
-        if self.sizes is not None:
-            if sum(self.sizes) != B or min(self.sizes) < 1:
-                raise ValueError(f"chunk sizes {self.sizes} do not cover a batch of {B}")
-            bounds = [sum(self.sizes[:i]) for i in range(len(self.sizes) + 1)]
-            schedule = list(zip(bounds[:-1], bounds[1:]))
-        else:
-            schedule = chunk_schedule(B, self.chunk)
-        for step, (b0, b1) in enumerate(schedule):
+        Hh = q.shape[2]
+        kept_coords = (None, None)       # (batch element, its coordinates on the device): shared by head groups
+        for step, (b0, b1, h0, h1) in enumerate(self._schedule(B, Hh)):
             s_comp = self.s_comps[step % len(self.s_comps)]
+            whole = h0 == 0 and h1 == Hh
             with torch.cuda.stream(self.s_in):
-                d_q, d_k, d_v, d_c = self._to_device((q, k, v, coords), b0, b1, s_comp)
+                if whole:
+                    d_q, d_k, d_v, d_c = self._to_device((q, k, v, coords), b0, b1, s_comp)
+                else:
+                    d_q, d_k, d_v = self._heads_to_device((q, k, v), b0, h0, h1, s_comp)
+                    if kept_coords[0] != b0:
+                        kept_coords = (b0, self._to_device((coords,), b0, b1, s_comp)[0])
+                    d_c = kept_coords[1]
+                    d_c.record_stream(s_comp)
                 ready_fwd = torch.cuda.Event()
                 ready_fwd.record(self.s_in)
-                (d_do,) = self._to_device((dout,), b0, b1, s_comp)
+                if whole:
+                    (d_do,) = self._to_device((dout,), b0, b1, s_comp)
+                else:
+                    (d_do,) = self._heads_to_device((dout,), b0, h0, h1, s_comp)
                 ready_bwd = torch.cuda.Event()
                 ready_bwd.record(self.s_in)
-            mirror = {n: results[n][b0:b1] for n in results if direct[n]}
+            mirror = {n: results[n][b0:b1] for n in results if direct[n]} if whole else {}
             copies = []
             s_comp.wait_event(ready_fwd)
             with torch.cuda.stream(s_comp):
                 o, lse = forward_raw(d_q, d_k, d_v, d_c, self.W, self.H, self.sm_scale, flags=self.flags,
                                      out_mirror=mirror.get("out"))
-                if not direct["out"]:
+                if "out" not in mirror:
                     fwd_done = torch.cuda.Event()
                     fwd_done.record(s_comp)
                     copies.append((fwd_done, out, o))
@@ -194,7 +283,7 @@ class HostPipeline:
                                          mirrors={n: t for n, t in mirror.items() if n != "out"} or None)
                     bwd_done = torch.cuda.Event()
                     bwd_done.record(s_comp)
-                    copies += [(bwd_done, results[n], g) for n, g in zip(("dq", "dk", "dv"), grads) if not direct[n]]
+                    copies += [(bwd_done, results[n], g) for n, g in zip(("dq", "dk", "dv"), grads) if n not in mirror]
             with torch.cuda.stream(self.s_out):
                 for event, host, dev_t in copies:
                     self.s_out.wait_event(event)
@@ -202,7 +291,11 @@ class HostPipeline:
                         marks["out0"].record(self.s_out)
                         first_out = False
                     dev_t.record_stream(self.s_out)
-                    host[b0:b1].copy_(dev_t, non_blocking=True)
+                    if whole:
+                        host[b0:b1].copy_(dev_t, non_blocking=True)
+                    else:
+                        for view in range(dev_t.shape[1]):
+                            host[b0, view, h0:h1].copy_(dev_t[0, view], non_blocking=True)
         if marks is not None:
             marks["in1"].record(self.s_in)
             marks["out1"].record(self.s_out)

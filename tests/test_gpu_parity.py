@@ -225,6 +225,32 @@ def test_host_pipeline_with_given_chunk_sizes(backend):
                                                                                dk=dk, dv=dv)
 
 
+@pytest.mark.parametrize("B,parts,results", [(5, 2, "pinned"), (1, 3, "pinned"), (2, 4, "pageable"), (3, 2, "pinned_direct")])
+def test_host_pipeline_with_head_groups_at_both_ends(backend, B, parts, results):
+    """The first and the last batch element cut into groups of heads (uneven ones too, a batch of
+    one where both ends are the same element): the same bits as the one-shot call.  With direct
+    result stores the cut is not made."""
+    from dataclasses import replace
+    cfg = replace(backend.inputs.CONFIGS["C2"], B=B, Hh=5)
+    q, k, v, coords, dout = backend.inputs.make_inputs(cfg, pin=True)
+    dev = torch.device("cuda", 0)
+    ref = _run(backend, (q, k, v, coords, dout), 0, cfg.dtype, cfg.W, cfg.H, cfg.sm_scale)
+    out, dq, dk, dv = (torch.zeros_like(q) for _ in range(4))
+    if results != "pageable":
+        out, dq, dk, dv = (t.pin_memory() for t in (out, dq, dk, dv))
+    pipe = backend.HostPipeline(dev, cfg.W, cfg.H, cfg.sm_scale, head_parts=parts,
+                                direct_results=results == "pinned_direct")
+    chunks = pipe._schedule(B, cfg.Hh)
+    if results == "pinned_direct":
+        assert all(h0 == 0 and h1 == cfg.Hh for _, _, h0, h1 in chunks)
+    else:
+        assert sum(1 for c in chunks if (c[2], c[3]) != (0, cfg.Hh)) == (parts if B == 1 else 2 * parts)
+    pipe.run(q, k, v, coords, dout, out=out, dq=dq, dk=dk, dv=dv)
+    torch.cuda.synchronize()
+    assert torch.equal(out, ref[0].cpu())
+    assert torch.equal(dq, ref[2].cpu()) and torch.equal(dk, ref[3].cpu()) and torch.equal(dv, ref[4].cpu())
+
+
 def test_link_probe_feeds_a_weighted_plan(backend):
     """The host-link probe returns two positive rates, and a plan weighted by them covers the
     batch with contiguous shards (one GPU: one rank's figures stand in for several)."""
