@@ -750,7 +750,7 @@ def main():
         e2e = {"value": cfg.query_heads / (e_ms * 1e-3), "unit": "query-heads/sec", "ms_per_step": e_ms,
                "h2d_bytes_per_step": h2d_all, "d2h_bytes_per_step": d2h_all,
                "chunks": [b1 - b0 if (h0, h1) == (0, cfg.Hh) else f"{h1 - h0}/{cfg.Hh} heads"
-                          for b0, b1, h0, h1 in pipe._schedule(e_nb, cfg.Hh)],
+                          for b0, b1, h0, h1 in pipe.schedule(e_nb, cfg.Hh)],
                "transfers_per_rank": per_rank}
         if shares is not None:
             e2e["batch_elements_per_rank"] = shares

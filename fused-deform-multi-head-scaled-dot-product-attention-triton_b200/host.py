@@ -196,7 +196,7 @@ class HostPipeline:
             out.append(d)
         return out
 
-    def _schedule(self, B: int, Hh: int):
+    def schedule(self, B: int, Hh: int):
         """Chunks as (b0, b1, h0, h1)."""
         if self.sizes is not None:
             if sum(self.sizes) != B or min(self.sizes) < 1:
@@ -246,7 +246,7 @@ class HostPipeline:
             first_out = True
         Hh = q.shape[2]
         kept_coords = (None, None)       # (batch element, its coordinates on the device): shared by head groups
-        for step, (b0, b1, h0, h1) in enumerate(self._schedule(B, Hh)):
+        for step, (b0, b1, h0, h1) in enumerate(self.schedule(B, Hh)):
             s_comp = self.s_comps[step % len(self.s_comps)]
             whole = h0 == 0 and h1 == Hh
             with torch.cuda.stream(self.s_in):

@@ -240,7 +240,7 @@ def test_host_pipeline_with_head_groups_at_both_ends(backend, B, parts, results)
         out, dq, dk, dv = (t.pin_memory() for t in (out, dq, dk, dv))
     pipe = backend.HostPipeline(dev, cfg.W, cfg.H, cfg.sm_scale, head_parts=parts,
                                 direct_results=results == "pinned_direct")
-    chunks = pipe._schedule(B, cfg.Hh)
+    chunks = pipe.schedule(B, cfg.Hh)
     if results == "pinned_direct":
         assert all(h0 == 0 and h1 == cfg.Hh for _, _, h0, h1 in chunks)
     else:
