@@ -131,6 +131,28 @@ def suggest_head_parts(link, in_bytes: float, out_bytes: float, compute_ms: floa
     return parts if _element_costs([link], in_bytes, out_bytes, compute_ms)[0] > float(compute_ms) else 1
 
 
+def pipeline_schedule(B: int, Hh: int, *, chunk: int = 8, sizes: Optional[Sequence[int]] = None, head_parts: int = 1):
+    """Chunks of a ``HostPipeline`` run as (b0, b1, h0, h1): ``chunk_schedule`` (or the given batch
+    ``sizes``) over the batch, with the first and the last chunk, when they are single batch
+    elements, cut into ``head_parts`` groups of heads (as even as the head count allows)."""
+    if sizes is not None:
+        if sum(sizes) != B or min(sizes) < 1:
+            raise ValueError(f"chunk sizes {list(sizes)} do not cover a batch of {B}")
+        bounds = [sum(sizes[:i]) for i in range(len(sizes) + 1)]
+        batches = list(zip(bounds[:-1], bounds[1:]))
+    else:
+        batches = chunk_schedule(B, chunk)
+    parts = min(max(1, int(head_parts)), Hh)
+    chunks = []
+    for i, (b0, b1) in enumerate(batches):
+        if parts > 1 and b1 - b0 == 1 and i in (0, len(batches) - 1):
+            cuts = [Hh * j // parts for j in range(parts + 1)]
+            chunks += [(b0, b1, h0, h1) for h0, h1 in zip(cuts[:-1], cuts[1:]) if h1 > h0]
+        else:
+            chunks.append((b0, b1, 0, Hh))
+    return chunks
+
+
 class HostPipeline:
     """Forward (+ backward) of the operator on host tensors, chunked over the batch.
 
@@ -198,24 +220,8 @@ class HostPipeline:
 
     def schedule(self, B: int, Hh: int):
         """Chunks as (b0, b1, h0, h1)."""
-        if self.sizes is not None:
-            if sum(self.sizes) != B or min(self.sizes) < 1:
-                raise ValueError(f"chunk sizes {self.sizes} do not cover a batch of {B}")
-            bounds = [sum(self.sizes[:i]) for i in range(len(self.sizes) + 1)]
-            batches = list(zip(bounds[:-1], bounds[1:]))
-        else:
-            batches = chunk_schedule(B, self.chunk)
-        parts = min(self.head_parts, Hh)
-        if self.direct_results:
-            parts = 1       # a head group is not a contiguous block of the result: no direct stores
-        chunks = []
-        for i, (b0, b1) in enumerate(batches):
-            if parts > 1 and b1 - b0 == 1 and i in (0, len(batches) - 1):
-                cuts = [Hh * j // parts for j in range(parts + 1)]
-                chunks += [(b0, b1, h0, h1) for h0, h1 in zip(cuts[:-1], cuts[1:]) if h1 > h0]
-            else:
-                chunks.append((b0, b1, 0, Hh))
-        return chunks
+        return pipeline_schedule(B, Hh, chunk=self.chunk, sizes=self.sizes,
+                                 head_parts=1 if self.direct_results else self.head_parts)
 
     def run(self, q, k, v, coords, dout=None, *, out, dq=None, dk=None, dv=None):
         """All arguments are host tensors (pinned for the copies to be asynchronous) with the
